@@ -1,0 +1,258 @@
+// Host side of the fused batch-norm (+ReLU) entry points: argument checks, the tile plan,
+// and the cooperative launch of the persistent kernels of bn_fused.cuh.
+#include "bn_host.h"
+
+namespace anode_b200 {
+
+// ---- tunables (read once; environment overrides exist for experiments only) --------------
+static uint32_t env_u32(const char *name, uint32_t dflt)
+{
+  const char *s = getenv(name);
+  if (!s || !*s) return dflt;
+  const long v = strtol(s, nullptr, 10);
+  return v > 0 ? (uint32_t)v : dflt;
+}
+
+const Tunables &tunables()
+{
+  static const Tunables t = {
+      env_u32("ANODE_B200_TILE_FLOATS", 8192),
+      env_u32("ANODE_B200_SLACK_STEPS", 1),
+      env_u32("ANODE_B200_BLOCKS_PER_SM", 4),
+  };
+  return t;
+}
+
+uint32_t sm_count()
+{
+  // one entry per device ordinal; 148 (B200) when no device can be queried, so that the
+  // planning helpers stay callable on a machine without a GPU
+  static std::atomic<int> cache[64];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { (void)cudaGetLastError(); return 148; }
+  int v = cache[dev].load(std::memory_order_relaxed);
+  if (v == 0) {
+    if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) {
+      (void)cudaGetLastError();
+      v = 148;
+    }
+    cache[dev].store(v, std::memory_order_relaxed);
+  }
+  return (uint32_t)v;
+}
+
+Plan plan_for(uint32_t dim0, uint32_t C, uint32_t N, bool aligned16)
+{
+  const Tunables &t = tunables();
+  return make_plan(dim0, C, N, aligned16, sm_count() * t.blocks_per_sm, t.tile_floats, t.slack_steps);
+}
+
+int check_dims(uint32_t dim0, uint32_t dim1, uint32_t dim2)
+{
+  if (dim0 == 0 || dim1 == 0 || dim2 == 0) return ANODE_E_DIMS;
+  const unsigned __int128 len = (unsigned __int128)dim0 * dim1 * dim2;
+  if (len >= ((unsigned __int128)1 << 32)) return ANODE_E_DIMS;
+  return ANODE_OK;
+}
+
+typedef void (*PipelineKernel)(const FusedArgs);
+
+static PipelineKernel pick_kernel(const Plan &p, int dir)
+{
+  if (p.regime == 1) return dir == 0 ? bn_pipeline_kernel<4, 0, 1> : bn_pipeline_kernel<4, 1, 1>;
+  if (p.vec == 4) return dir == 0 ? bn_pipeline_kernel<4, 0, 0> : bn_pipeline_kernel<4, 1, 0>;
+  return dir == 0 ? bn_pipeline_kernel<1, 0, 0> : bn_pipeline_kernel<1, 1, 0>;
+}
+
+// Blocks of `k` that fit on one SM (cached per kernel; same answer on every B200).
+static uint32_t blocks_per_sm(PipelineKernel k)
+{
+  static std::mutex mu;
+  static std::map<const void *, int> cache;
+  std::lock_guard<std::mutex> lock(mu);
+  auto it = cache.find((const void *)k);
+  if (it != cache.end()) return (uint32_t)it->second;
+  int n = 0;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, k, (int)kThreads, 0) != cudaSuccess) { (void)cudaGetLastError(); n = 0; }
+  cache[(const void *)k] = n;
+  return (uint32_t)n;
+}
+
+int launch_pipeline(FusedArgs &a, int dir, cudaStream_t stream)
+{
+  PipelineKernel k = pick_kernel(a.plan, dir);
+  const uint32_t fit = blocks_per_sm(k) * sm_count();
+  if (fit == 0) return ANODE_E_LAUNCH;
+  if (a.plan.grid > fit) {
+    // fewer blocks are resident than planned: shrink the grid and re-derive the lookahead
+    a.plan.grid = fit;
+    a.plan.lookahead_steps = ceil_div_u32(a.plan.tiles_per_unit, a.plan.grid) + tunables().slack_steps;
+  }
+  void *params[] = {(void *)&a};
+  cudaError_t e;
+  if (a.mode == MODE_FUSED) {
+    // Blocks wait on one another's results, so all of them must be resident: a cooperative
+    // launch fails instead of deadlocking when they would not be.
+    e = cudaLaunchCooperativeKernel((const void *)k, dim3(a.plan.grid), dim3(kThreads), params, 0, stream);
+  } else {
+    e = cudaLaunchKernel((const void *)k, dim3(a.plan.grid), dim3(kThreads), params, 0, stream);
+  }
+  if (e != cudaSuccess) { (void)cudaGetLastError(); return ANODE_E_LAUNCH; }
+  return ANODE_OK;
+}
+
+bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+bool aligned4(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 3u) == 0; }
+
+int prepare_fwd(FusedArgs &a, uint32_t dim0, uint32_t dim1, uint32_t dim2, float epsilon, float avg_rate,
+                int relu, const float *x, const float *gamma, const float *beta, float *y, float *mean,
+                float *var, float *run_mean, float *run_var, void *ws, size_t ws_bytes)
+{
+  const int rc = check_dims(dim0, dim1, dim2);
+  if (rc) return rc;
+  if (!x || !y || !mean || !var) return ANODE_E_NULL;
+  if (!aligned4(x) || !aligned4(y)) return ANODE_E_ALIGN;
+  if (!ws || !aligned16(ws)) return ANODE_E_WORKSPACE;
+  a = FusedArgs{};
+  a.plan = plan_for(dim0, dim1, dim2, aligned16(x) && aligned16(y));
+  if (ws_bytes < a.plan.ws_bytes) return ANODE_E_WORKSPACE;
+  a.x = x; a.gamma = gamma; a.beta = beta; a.out = y;
+  a.mean = mean; a.var = var; a.run_mean = run_mean; a.run_var = run_var;
+  a.ws = static_cast<unsigned char *>(ws);
+  a.epsilon = epsilon; a.avg_rate = avg_rate; a.relu = relu ? 1u : 0u;
+  a.mode = MODE_FUSED;
+  a.count_total = (double)dim0 * (double)dim2;
+  return ANODE_OK;
+}
+
+int prepare_bwd(FusedArgs &a, uint32_t dim0, uint32_t dim1, uint32_t dim2, int relu, int accumulate,
+                const float *dy, const float *x, const float *mean, const float *var, const float *gamma,
+                const float *beta, float *dx, float *dgamma, float *dbeta, void *ws, size_t ws_bytes)
+{
+  const int rc = check_dims(dim0, dim1, dim2);
+  if (rc) return rc;
+  if (!x || !dy || !dx || !mean || !var) return ANODE_E_NULL;
+  if (!aligned4(x) || !aligned4(dy) || !aligned4(dx)) return ANODE_E_ALIGN;
+  if (!ws || !aligned16(ws)) return ANODE_E_WORKSPACE;
+  a = FusedArgs{};
+  a.plan = plan_for(dim0, dim1, dim2, aligned16(x) && aligned16(dy) && aligned16(dx));
+  if (ws_bytes < a.plan.ws_bytes) return ANODE_E_WORKSPACE;
+  a.x = x; a.dy = dy; a.gamma = gamma; a.beta = beta; a.mean_in = mean; a.var_in = var;
+  a.out = dx; a.dgamma = dgamma; a.dbeta = dbeta;
+  a.ws = static_cast<unsigned char *>(ws);
+  a.relu = relu ? 1u : 0u; a.accumulate = accumulate ? 1u : 0u;
+  a.mode = MODE_FUSED;
+  a.count_total = (double)dim0 * (double)dim2;
+  return ANODE_OK;
+}
+
+__global__ void online_average_kernel(uint32_t len, float rate, const float *x, float *y)
+{
+  for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < len; i += gridDim.x * blockDim.x) {
+    const float o = y[i];
+    y[i] = o + rate * (x[i] - o);
+  }
+}
+
+}  // namespace anode_b200
+
+using namespace anode_b200;
+
+extern "C" size_t anode_gpu_batch_norm_fused_workspace_bytes(uint32_t dim0, uint32_t dim1, uint32_t dim2)
+{
+  if (check_dims(dim0, dim1, dim2)) return 0;
+  // the plan depends on pointer alignment, which is not known yet: cover both cases
+  const Plan a = plan_for(dim0, dim1, dim2, true), b = plan_for(dim0, dim1, dim2, false);
+  return (size_t)(a.ws_bytes > b.ws_bytes ? a.ws_bytes : b.ws_bytes);
+}
+
+extern "C" int anode_gpu_batch_norm_fused_workspace_init(void *workspace, size_t bytes, struct CUstream_st *stream)
+{
+  if (!workspace) return ANODE_E_NULL;
+  if (cudaMemsetAsync(workspace, 0, bytes, stream) != cudaSuccess) { (void)cudaGetLastError(); return ANODE_E_LAUNCH; }
+  return ANODE_OK;
+}
+
+extern "C" int anode_gpu_batch_norm_fused_status(const void *workspace, struct CUstream_st *stream, uint32_t *status)
+{
+  if (!workspace || !status) return ANODE_E_NULL;
+  if (cudaMemcpyAsync(status, workspace, sizeof(uint32_t), cudaMemcpyDeviceToHost, stream) != cudaSuccess ||
+      cudaStreamSynchronize(stream) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return ANODE_E_LAUNCH;
+  }
+  return ANODE_OK;
+}
+
+extern "C" int anode_gpu_batch_norm_relu_fused_fwd_3d1_packed_f32(
+    uint32_t dim0, uint32_t dim1, uint32_t dim2, float epsilon, float avg_rate, int relu,
+    const float *x, const float *gamma, const float *beta,
+    float *y, float *mean, float *var, float *run_mean, float *run_var,
+    void *workspace, size_t workspace_bytes, const struct KernelConfig *cfg, struct CUstream_st *stream)
+{
+  (void)cfg;
+  FusedArgs a;
+  const int rc = prepare_fwd(a, dim0, dim1, dim2, epsilon, avg_rate, relu, x, gamma, beta, y, mean, var,
+                             run_mean, run_var, workspace, workspace_bytes);
+  if (rc) return rc;
+  return launch_pipeline(a, 0, stream);
+}
+
+extern "C" int anode_gpu_batch_norm_relu_fused_bwd_3d1_packed_f32(
+    uint32_t dim0, uint32_t dim1, uint32_t dim2, int relu, int accumulate,
+    const float *dy, const float *x, const float *mean, const float *var,
+    const float *gamma, const float *beta, float *dx, float *dgamma, float *dbeta,
+    void *workspace, size_t workspace_bytes, const struct KernelConfig *cfg, struct CUstream_st *stream)
+{
+  (void)cfg;
+  FusedArgs a;
+  const int rc = prepare_bwd(a, dim0, dim1, dim2, relu, accumulate, dy, x, mean, var, gamma, beta, dx,
+                             dgamma, dbeta, workspace, workspace_bytes);
+  if (rc) return rc;
+  return launch_pipeline(a, 1, stream);
+}
+
+extern "C" int anode_gpu_online_average_f32(uint32_t len, float rate, const float *x, float *y,
+                                            const struct KernelConfig *cfg, struct CUstream_st *stream)
+{
+  (void)cfg;
+  if (!x || !y) return ANODE_E_NULL;
+  if (len == 0) return ANODE_OK;
+  const uint32_t blocks = (len + 255) / 256 < 1184 ? (len + 255) / 256 : 1184;
+  online_average_kernel<<<blocks, 256, 0, stream>>>(len, rate, x, y);
+  if (cudaGetLastError() != cudaSuccess) return ANODE_E_LAUNCH;
+  return ANODE_OK;
+}
+
+// ---- diagnostics: the tile plan, for tests of the index arithmetic (no GPU needed) ----------
+extern "C" int anode_gpu_batch_norm_fused_plan(uint32_t dim0, uint32_t dim1, uint32_t dim2, int aligned,
+                                               uint32_t resident_blocks, uint32_t tile_floats,
+                                               uint32_t slack_steps, uint32_t *out, uint32_t out_len)
+{
+  if (!out || check_dims(dim0, dim1, dim2)) return ANODE_E_DIMS;
+  const Tunables &t = tunables();
+  const Plan p = make_plan(dim0, dim1, dim2, aligned != 0,
+                           resident_blocks ? resident_blocks : sm_count() * t.blocks_per_sm,
+                           tile_floats ? tile_floats : t.tile_floats, slack_steps ? slack_steps : t.slack_steps);
+  const uint32_t v[] = {p.regime, p.vec, p.cb, p.units, p.rows_per_tile, p.piece_len, p.pieces,
+                        p.sample_blocks, p.tiles_per_unit, p.total_tiles, p.grid, p.lookahead_steps,
+                        p.div_mul, (uint32_t)(p.ws_bytes & 0xffffffffu), (uint32_t)(p.ws_bytes >> 32)};
+  for (uint32_t i = 0; i < out_len && i < sizeof(v) / sizeof(v[0]); ++i) out[i] = v[i];
+  return ANODE_OK;
+}
+
+extern "C" int anode_gpu_batch_norm_fused_plan_tile(uint32_t dim0, uint32_t dim1, uint32_t dim2, int aligned,
+                                                    uint32_t resident_blocks, uint32_t tile_floats,
+                                                    uint32_t tile, uint64_t *out)
+{
+  if (!out || check_dims(dim0, dim1, dim2)) return ANODE_E_DIMS;
+  const Tunables &t = tunables();
+  const Plan p = make_plan(dim0, dim1, dim2, aligned != 0,
+                           resident_blocks ? resident_blocks : sm_count() * t.blocks_per_sm,
+                           tile_floats ? tile_floats : t.tile_floats, t.slack_steps);
+  if (tile >= p.total_tiles) return ANODE_E_DIMS;
+  const TileRange r = tile_range(p, tile);
+  out[0] = r.unit; out[1] = r.c0; out[2] = r.cw; out[3] = r.n0; out[4] = r.rows; out[5] = r.col0;
+  out[6] = r.len; out[7] = r.base;
+  return ANODE_OK;
+}

@@ -1,0 +1,37 @@
+// Host-side declarations shared by the translation units of libanode_routines_gpu.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdlib.h>
+
+#include <atomic>
+#include <map>
+#include <mutex>
+
+#include "../../include/anode_routines_gpu.h"
+#include "bn_fused.cuh"
+
+namespace anode_b200 {
+
+struct Tunables {
+  uint32_t tile_floats;     // target floats per tile
+  uint32_t slack_steps;     // extra lookahead steps beyond the minimum
+  uint32_t blocks_per_sm;   // persistent blocks planned per SM
+};
+const Tunables &tunables();
+
+uint32_t sm_count();
+Plan plan_for(uint32_t dim0, uint32_t C, uint32_t N, bool aligned16);
+int check_dims(uint32_t dim0, uint32_t dim1, uint32_t dim2);
+bool aligned16(const void *p);
+bool aligned4(const void *p);
+
+int prepare_fwd(FusedArgs &a, uint32_t dim0, uint32_t dim1, uint32_t dim2, float epsilon, float avg_rate,
+                int relu, const float *x, const float *gamma, const float *beta, float *y, float *mean,
+                float *var, float *run_mean, float *run_var, void *ws, size_t ws_bytes);
+int prepare_bwd(FusedArgs &a, uint32_t dim0, uint32_t dim1, uint32_t dim2, int relu, int accumulate,
+                const float *dy, const float *x, const float *mean, const float *var, const float *gamma,
+                const float *beta, float *dx, float *dgamma, float *dbeta, void *ws, size_t ws_bytes);
+int launch_pipeline(FusedArgs &a, int dir, cudaStream_t stream);
+
+}  // namespace anode_b200

@@ -1,0 +1,232 @@
+/*
+ * C ABI of libanode_routines_gpu (sm_100a build): the batch-norm / ReLU slice of anode's
+ * GPU routine library, plus fused and multi-GPU entry points in the same style.
+ *
+ * Drop-in contract.  The first block below re-declares, name for name and argument for
+ * argument, the symbols anode's Rust side binds through bindgen (reference
+ * routines_gpu/lib.h, whitelist in build.rs:65-82 and :91-106, used from src/ops_gpu.rs via
+ * src/ffi.rs:35).  An existing anode build that links this library instead of its own
+ * routines for these symbols keeps working unchanged.
+ *
+ * Conventions shared by every entry point (reference src/ops_gpu.rs:3763-3771):
+ *   - arrays are packed f32; element (i0, c, n) of a [dim0, dim1, dim2] array is at
+ *     i0 + dim0*(c + dim1*n): dim0 = product of the spatial sizes, dim1 = channels,
+ *     dim2 = batch.  That is a contiguous NCHW / NCDHW tensor.
+ *   - every pointer is a device pointer owned by the caller; the callee allocates nothing,
+ *     frees nothing and keeps no state between calls;
+ *   - work is enqueued on `stream` and the call returns at once (no device synchronisation);
+ *   - `cfg` is the caller's launch-shape hint {block_sz, max_block_ct}
+ *     (routines_gpu/common.cuh:51-67).  It may be NULL.  The kernels here choose their own
+ *     launch shapes and only read it to honour the power-of-two contract of the reduce
+ *     kernels (routines_gpu/batch_norm.cu:68);
+ *   - `_accumulate_` twins add into the destination (WriteCap::Accumulate,
+ *     routines_gpu/common.cuh:188-193); the others overwrite it;
+ *   - dim0*dim1*dim2 must be below 2^32 (the callers' sz2uint, src/ops_gpu.rs:57-61).
+ */
+#ifndef ANODE_ROUTINES_GPU_B200_H
+#define ANODE_ROUTINES_GPU_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+struct CUstream_st;
+
+/* routines_gpu/common.cuh:51-67 (data members); Rust mirror src/ffi.rs:28-33. */
+struct KernelConfig {
+  uint32_t block_sz;
+  uint32_t max_block_ct;
+};
+
+/* ===================================================================================
+ * 1. The reference's own entry points (same names, same signatures, same semantics).
+ * =================================================================================== */
+
+/* routines_gpu/lib.h:32-39 / batch_norm.cu:59-71.  mean[c] = sum(x) / (dim0*dim2). */
+void anode_gpu_batch_mean_3d1_packed_f32(
+    uint32_t dim0, uint32_t dim1, uint32_t dim2,
+    const float *x, float *mean,
+    const struct KernelConfig *cfg, struct CUstream_st *stream);
+
+/* lib.h:40-55 / batch_norm.cu:97-123.  dx (+)= dmean[c] / (dim0*dim2). */
+void anode_gpu_batch_mean_bwd_3d1_packed_f32(
+    uint32_t dim0, uint32_t dim1, uint32_t dim2,
+    const float *dmean, float *dx,
+    const struct KernelConfig *cfg, struct CUstream_st *stream);
+void anode_gpu_batch_mean_bwd_3d1_packed_accumulate_f32(
+    uint32_t dim0, uint32_t dim1, uint32_t dim2,
+    const float *dmean, float *dx,
+    const struct KernelConfig *cfg, struct CUstream_st *stream);
+
+/* lib.h:56-65 / batch_norm.cu:165-179.  var[c] = sum((x-mean[c])^2)/(dim0*dim2) + epsilon
+ * (biased; epsilon is folded into the stored value). */
+void anode_gpu_batch_var_3d1_packed_f32(
+    uint32_t dim0, uint32_t dim1, uint32_t dim2, float epsilon,
+    const float *x, const float *mean, float *var,
+    const struct KernelConfig *cfg, struct CUstream_st *stream);
+
+/* lib.h:66-85 / batch_norm.cu:208-238.  dx (+)= dvar[c]*(x-mean[c])*2/(dim0*dim2). */
+void anode_gpu_batch_var_bwd_3d1_packed_f32(
+    uint32_t dim0, uint32_t dim1, uint32_t dim2,
+    const float *dvar, const float *x, const float *mean, float *dx,
+    const struct KernelConfig *cfg, struct CUstream_st *stream);
+void anode_gpu_batch_var_bwd_3d1_packed_accumulate_f32(
+    uint32_t dim0, uint32_t dim1, uint32_t dim2,
+    const float *dvar, const float *x, const float *mean, float *dx,
+    const struct KernelConfig *cfg, struct CUstream_st *stream);
+
+/* lib.h:86-105 / batch_norm.cu:282-312.  dmean[c] (+)= sum((x-mean[c])*(-2*dvar[c]))/(dim0*dim2). */
+void anode_gpu_batch_var_bwd_mean_3d1_packed_f32(
+    uint32_t dim0, uint32_t dim1, uint32_t dim2,
+    const float *dvar, const float *x, const float *mean, float *dmean,
+    const struct KernelConfig *cfg, struct CUstream_st *stream);
+void anode_gpu_batch_var_bwd_mean_3d1_packed_accumulate_f32(
+    uint32_t dim0, uint32_t dim1, uint32_t dim2,
+    const float *dvar, const float *x, const float *mean, float *dmean,
+    const struct KernelConfig *cfg, struct CUstream_st *stream);
+
+/* lib.h:106-115 / batch_norm.cu:338-352.  y = (x-mean[c]) * rsqrt(var[c]). */
+void anode_gpu_batch_norm_3d1_packed_f32(
+    uint32_t dim0, uint32_t dim1, uint32_t dim2,
+    const float *x, const float *mean, const float *var, float *y,
+    const struct KernelConfig *cfg, struct CUstream_st *stream);
+
+/* lib.h:116-133 / batch_norm.cu:378-406.  dx (+)= dy * rsqrt(var[c]). */
+void anode_gpu_batch_norm_bwd_3d1_packed_f32(
+    uint32_t dim0, uint32_t dim1, uint32_t dim2,
+    const float *dy, const float *var, float *dx,
+    const struct KernelConfig *cfg, struct CUstream_st *stream);
+void anode_gpu_batch_norm_bwd_3d1_packed_accumulate_f32(
+    uint32_t dim0, uint32_t dim1, uint32_t dim2,
+    const float *dy, const float *var, float *dx,
+    const struct KernelConfig *cfg, struct CUstream_st *stream);
+
+/* lib.h:134-151 / batch_norm.cu:446-474.  dmean[c] (+)= sum(dy) * (-rsqrt(var[c])). */
+void anode_gpu_batch_norm_bwd_mean_3d1_packed_f32(
+    uint32_t dim0, uint32_t dim1, uint32_t dim2,
+    const float *dy, const float *var, float *dmean,
+    const struct KernelConfig *cfg, struct CUstream_st *stream);
+void anode_gpu_batch_norm_bwd_mean_3d1_packed_accumulate_f32(
+    uint32_t dim0, uint32_t dim1, uint32_t dim2,
+    const float *dy, const float *var, float *dmean,
+    const struct KernelConfig *cfg, struct CUstream_st *stream);
+
+/* lib.h:152-173 / batch_norm.cu:517-549.
+ * dvar[c] (+)= sum(dy*(x-mean[c])) * (-0.5*rsqrt(var[c])/var[c]). */
+void anode_gpu_batch_norm_bwd_var_3d1_packed_f32(
+    uint32_t dim0, uint32_t dim1, uint32_t dim2,
+    const float *dy, const float *x, const float *mean, const float *var, float *dvar,
+    const struct KernelConfig *cfg, struct CUstream_st *stream);
+void anode_gpu_batch_norm_bwd_var_3d1_packed_accumulate_f32(
+    uint32_t dim0, uint32_t dim1, uint32_t dim2,
+    const float *dy, const float *x, const float *mean, const float *var, float *dvar,
+    const struct KernelConfig *cfg, struct CUstream_st *stream);
+
+/* lib.h:174-193 / batch_norm.cu:589-619.  dvar[c] (+)= sum(-dy*y*0.5/var[c]), y the
+ * normalized output saved from the forward pass. */
+void anode_gpu_batch_norm_bwd_var_v2_3d1_packed_f32(
+    uint32_t dim0, uint32_t dim1, uint32_t dim2,
+    const float *dy, const float *y, const float *var, float *dvar,
+    const struct KernelConfig *cfg, struct CUstream_st *stream);
+void anode_gpu_batch_norm_bwd_var_v2_3d1_packed_accumulate_f32(
+    uint32_t dim0, uint32_t dim1, uint32_t dim2,
+    const float *dy, const float *y, const float *var, float *dvar,
+    const struct KernelConfig *cfg, struct CUstream_st *stream);
+
+/* lib.h:296-302 / flat_join.cu:50-60.  y = x1 * (float)(x2 > 0). */
+void anode_gpu_M1_copy_map_M2_unit_step_map_R_product_reduce_flat_join_f32(
+    uint32_t len, const float *x1, const float *x2, float *y,
+    const struct KernelConfig *cfg, struct CUstream_st *stream);
+
+/* lib.h:344-349 / flat_map.cu:392-401.  y = x * (float)(x > 0); y may alias x
+ * (src/ops_gpu.rs:7912-7918). */
+void anode_gpu_positive_clip_flat_map_f32(
+    uint32_t len, const float *x, float *y,
+    const struct KernelConfig *cfg, struct CUstream_st *stream);
+
+/* lib.h:350-356 / flat_map.cu:403-413.  dx = dy * (float)(y > 0); dx may alias dy
+ * (src/ops_gpu.rs:7929-7939). */
+void anode_gpu_positive_clip_flat_map_bwd_f32(
+    uint32_t len, const float *dy, const float *y, float *dx,
+    const struct KernelConfig *cfg, struct CUstream_st *stream);
+
+/* ===================================================================================
+ * 2. Fused batch-norm + ReLU (new; backs BatchNormalize{2,3}dFusedOp and
+ *    BatchNormalize{2,3}dBwdFusedOp, which src/ops.rs:105-106 declares but never builds).
+ *
+ * One launch per direction replaces the reference's eleven (src/ops.rs:999-1014 forward,
+ * src/ops_gpu.rs:4344-4352, 3997-4003, 3787-3791 backward, flat_map.cu:392-413 ReLU).
+ *
+ * Return value: 0 on success, a negative ANODE_E_* code when the arguments are rejected
+ * before anything is enqueued.  Run-time trouble inside the kernel (a bounded wait that
+ * ran out) is reported through the status word read by anode_gpu_batch_norm_fused_status.
+ * =================================================================================== */
+
+#define ANODE_OK            0
+#define ANODE_E_NULL       -1   /* a required pointer is NULL */
+#define ANODE_E_DIMS       -2   /* a dimension is 0 or dim0*dim1*dim2 >= 2^32 */
+#define ANODE_E_WORKSPACE  -3   /* workspace missing, misaligned or too small */
+#define ANODE_E_LAUNCH     -4   /* the CUDA runtime refused the launch */
+#define ANODE_E_COMM       -5   /* communicator missing / inconsistent / NCCL failure */
+#define ANODE_E_ALIGN      -6   /* tensor pointers must be 4-byte aligned */
+
+/* Bits of the device status word. */
+#define ANODE_ST_WAIT_STATS   1u  /* a wait for a channel's statistics ran out */
+#define ANODE_ST_WAIT_PEER    2u  /* a wait for another GPU's partials ran out */
+#define ANODE_ST_ABORTED      4u  /* some block saw the bits above and skipped work */
+
+/* Scratch the fused kernels need for a [dim0, dim1, dim2] problem: per-tile partial
+ * statistics, per-channel coefficients, progress counters.  A few hundred KB. */
+size_t anode_gpu_batch_norm_fused_workspace_bytes(uint32_t dim0, uint32_t dim1, uint32_t dim2);
+
+/* Zeroes a workspace (cudaMemsetAsync on `stream`).  Needed once after allocation and after
+ * any call whose status word came back non-zero; the kernels leave the workspace clean
+ * otherwise, so back-to-back launches on one stream may share it. */
+int anode_gpu_batch_norm_fused_workspace_init(void *workspace, size_t bytes, struct CUstream_st *stream);
+
+/* Copies the status word of a workspace to the host (synchronises `stream`). 0 = clean. */
+int anode_gpu_batch_norm_fused_status(const void *workspace, struct CUstream_st *stream, uint32_t *status);
+
+/* Forward, training mode:
+ *   mean[c] = sum(x)/M                              M = dim0*dim2
+ *   var[c]  = sum((x-mean)^2)/M + epsilon           (biased, epsilon folded in, as anode stores it)
+ *   run_mean += avg_rate*(mean - run_mean); run_var += avg_rate*(var - run_var)
+ *                                                   (skipped when the pointer is NULL)
+ *   y = relu(gamma[c]*(x-mean[c])*var[c]^-1/2 + beta[c])
+ * gamma == NULL means no affine (the reference's behaviour); beta may be NULL with gamma set.
+ * relu == 0 leaves out the ReLU.  x and y may alias. */
+int anode_gpu_batch_norm_relu_fused_fwd_3d1_packed_f32(
+    uint32_t dim0, uint32_t dim1, uint32_t dim2,
+    float epsilon, float avg_rate, int relu,
+    const float *x, const float *gamma, const float *beta,
+    float *y, float *mean, float *var, float *run_mean, float *run_var,
+    void *workspace, size_t workspace_bytes,
+    const struct KernelConfig *cfg, struct CUstream_st *stream);
+
+/* Backward of the above.  The ReLU mask is recomputed from x (y is not read):
+ *   dz = dy * (gamma*xhat + beta > 0)         xhat = (x-mean)*var^-1/2
+ *   dbeta = sum(dz), dgamma = sum(dz*xhat)    (written when the pointers are non-NULL)
+ *   dx = gamma*var^-1/2 * (dz - dbeta/M - xhat*dgamma/M)
+ * which is the closed form of the reference's dvar/dmean/dx kernel chain.
+ * accumulate != 0 adds into dx instead of overwriting it.  dx may alias dy. */
+int anode_gpu_batch_norm_relu_fused_bwd_3d1_packed_f32(
+    uint32_t dim0, uint32_t dim1, uint32_t dim2, int relu, int accumulate,
+    const float *dy, const float *x, const float *mean, const float *var,
+    const float *gamma, const float *beta,
+    float *dx, float *dgamma, float *dbeta,
+    void *workspace, size_t workspace_bytes,
+    const struct KernelConfig *cfg, struct CUstream_st *stream);
+
+/* Running-statistic update on its own (OnlineAverageOp, src/ops_gpu.rs:6034-6077; rule
+ * pinned by tests/test_gpu.rs:561-593):  y[i] += rate*(x[i] - y[i]). */
+int anode_gpu_online_average_f32(
+    uint32_t len, float rate, const float *x, float *y,
+    const struct KernelConfig *cfg, struct CUstream_st *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

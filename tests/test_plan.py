@@ -1,0 +1,82 @@
+"""Host logic of the fused kernels: the tile plan covers every element exactly once, the
+fast division is exact where it is used, and the lookahead rule that makes the in-kernel
+wait cycle-free holds.  Runs on CPU through the planner's diagnostic entry points."""
+import ctypes
+
+import numpy as np
+import pytest
+
+from anode_b200 import _lib
+
+FIELDS = ["regime", "vec", "cb", "units", "rows_per_tile", "piece_len", "pieces", "sample_blocks",
+          "tiles_per_unit", "total_tiles", "grid", "lookahead_steps", "div_mul", "ws_lo", "ws_hi"]
+
+
+def plan(d0, c, n, aligned=True, resident=592, tile_floats=8192, slack=1):
+    out = (ctypes.c_uint32 * len(FIELDS))()
+    rc = _lib.load().anode_gpu_batch_norm_fused_plan(d0, c, n, int(aligned), resident, tile_floats, slack, out, len(FIELDS))
+    assert rc == 0
+    return dict(zip(FIELDS, list(out)))
+
+
+def tile(d0, c, n, t, aligned=True, resident=592, tile_floats=8192):
+    out = (ctypes.c_uint64 * 8)()
+    rc = _lib.load().anode_gpu_batch_norm_fused_plan_tile(d0, c, n, int(aligned), resident, tile_floats, t, out)
+    assert rc == 0
+    return dict(zip(["unit", "c0", "cw", "n0", "rows", "col0", "len", "base"], list(out)))
+
+
+SHAPES = [(784, 64, 32), (12544, 6, 8), (3136, 8, 16), (49, 96, 64), (49, 3, 5), (1, 2, 3), (1, 1, 1),
+          (117, 5, 7), (15, 260, 33), (16, 8, 4), (40800, 3, 2), (288, 4, 2), (262144, 2, 1), (49, 2048, 16),
+          (500, 4, 3), (65536, 1, 2), (255, 4, 9), (511, 8, 2)]
+
+
+@pytest.mark.parametrize("d0,c,n", SHAPES)
+@pytest.mark.parametrize("aligned", [True, False])
+def test_tiles_cover_every_element_once(d0, c, n, aligned):
+    p = plan(d0, c, n, aligned, resident=64, tile_floats=2048)
+    cover = np.zeros(d0 * c * n, np.int32)
+    for t in range(p["total_tiles"]):
+        r = tile(d0, c, n, t, aligned, resident=64, tile_floats=2048)
+        assert r["unit"] == t // p["tiles_per_unit"]
+        assert r["rows"] * r["len"] <= 65532
+        if p["vec"] == 4:
+            assert r["len"] % 4 == 0 and r["base"] % 4 == 0 and (c * d0) % 4 == 0 or r["rows"] == 1
+            assert r["len"] % 4 == 0 and r["base"] % 4 == 0
+        for k in range(r["rows"]):
+            lo = r["base"] + k * c * d0
+            cover[lo:lo + r["len"]] += 1
+            # the tile stays inside its unit's channels
+            first_c = (lo // d0) % c
+            last_c = ((lo + r["len"] - 1) // d0) % c
+            assert r["c0"] <= first_c <= last_c < r["c0"] + r["cw"]
+    assert (cover == 1).all()
+    if p["vec"] == 4 and p["regime"] == 1:
+        assert p["cb"] * d0 <= 2048 and p["cb"] <= 256
+    # wait-freedom of the pipeline: a block reduces tile i + lookahead*grid before applying tile i
+    assert p["lookahead_steps"] * p["grid"] >= p["tiles_per_unit"]
+    assert p["grid"] <= 64 and p["grid"] <= p["total_tiles"]
+
+
+def test_benchmark_shapes_pick_the_expected_regimes():
+    assert plan(12544, 64, 256)["regime"] == 0 and plan(12544, 64, 256)["vec"] == 4      # config 2
+    assert plan(3136, 256, 256)["vec"] == 4                                              # config 3 / 8 GPUs
+    assert plan(262144, 32, 4)["pieces"] > 1                                             # config 4 / 8 GPUs
+    p5 = plan(49, 2048, 128)                                                             # config 5 / 8 GPUs
+    assert p5["regime"] == 1 and p5["cb"] % 4 == 0 and p5["cb"] * 49 > 0.9 * 2048
+    assert plan(49, 3, 5)["vec"] == 1                                                    # nothing aligns: scalar
+
+
+def test_fast_division_is_exact_in_its_domain():
+    # q = (n * mul) >> 32 with mul = floor(2^32/d) + 1 must equal n // d for every vector index of a
+    # tile: n < rows*d <= 65532
+    rng = np.random.default_rng(0)
+    ds = np.unique(np.concatenate([np.arange(1, 300), rng.integers(300, 65532, 400), [16383, 32766, 65532]]))
+    for d in ds:
+        mul = (1 << 32) // int(d) + 1
+        rows = 65532 // int(d)
+        n = np.arange(0, rows * int(d), dtype=np.uint64)
+        if n.size > 20000:
+            n = np.unique(np.concatenate([n[:5000], n[-5000:], rng.choice(n, 5000)]))
+        q = (n * np.uint64(mul)) >> np.uint64(32)
+        assert (q == n // np.uint64(d)).all(), d

@@ -1,0 +1,83 @@
+"""Shared helpers of the test-suite: seeded inputs of the benchmark configurations and the
+tolerance rules.
+
+Tolerance (the parity bar of this path): |got - want| <= 1e-5 + 1e-4*|want| on y, dx, mean,
+var and the running statistics.  Two refinements, both stated where used:
+  * elements whose pre-activation gamma*xhat+beta is within 1e-5 of zero are skipped in y/dx:
+    there the ReLU mask legitimately depends on the last bit of the statistics;
+  * per-channel sums (dgamma, dbeta) are compared with atol = 1e-5 + 1e-4*rms(want), since a
+    sum of M terms that happens to cancel has no meaningful relative error.
+"""
+import numpy as np
+
+RTOL, ATOL = 1e-4, 1e-5
+
+
+def make_inputs(shape, seed, dist="normal", loc=0.0, scale=1.0, affine=True):
+    """x, dy, gamma, beta, run_mean, run_var as the benchmark configurations define them:
+    x ~ N(loc, scale) or scale*Student-t(3); dy ~ N(0,1); gamma ~ U(0.5,1.5); beta ~ U(-0.1,0.1);
+    running mean 0, running variance 1."""
+    rng = np.random.default_rng(seed)
+    if dist == "normal":
+        x = rng.standard_normal(shape, dtype=np.float32) * np.float32(scale) + np.float32(loc)
+    elif dist == "student3":
+        x = (rng.standard_t(3, size=shape) * scale).astype(np.float32)
+    else:
+        raise ValueError(dist)
+    dy = rng.standard_normal(shape, dtype=np.float32)
+    c = shape[1]
+    gamma = rng.uniform(0.5, 1.5, c).astype(np.float32) if affine else None
+    beta = rng.uniform(-0.1, 0.1, c).astype(np.float32) if affine else None
+    return dict(x=x, dy=dy, gamma=gamma, beta=beta,
+                run_mean=np.zeros(c, np.float32), run_var=np.ones(c, np.float32))
+
+
+def close(got, want, rtol=RTOL, atol=ATOL):
+    got = np.asarray(got, dtype=np.float64)
+    want = np.asarray(want, dtype=np.float64)
+    return np.abs(got - want) <= atol + rtol * np.abs(want)
+
+
+def assert_close(got, want, what, rtol=RTOL, atol=ATOL, skip=None):
+    ok = close(got, want, rtol, atol)
+    if skip is not None:
+        ok = ok | skip
+    if not ok.all():
+        got = np.asarray(got, dtype=np.float64)
+        want = np.asarray(want, dtype=np.float64)
+        bad = np.argwhere(~ok)
+        i = tuple(bad[0])
+        raise AssertionError("%s: %d of %d elements off; first at %s: got %r want %r (max abs diff %g)" % (
+            what, len(bad), ok.size, i, got[i], want[i], np.abs(got - want)[~ok].max()))
+
+
+def assert_sum_close(got, want, what):
+    want = np.asarray(want, dtype=np.float64)
+    rms = float(np.sqrt(np.mean(want * want))) if want.size else 0.0
+    assert_close(got, want, what, rtol=RTOL, atol=ATOL + RTOL * rms)
+
+
+def borderline(truth, x, gamma, beta, tol=1e-5):
+    """Elements whose pre-activation is within tol of zero (mask undecidable in f32)."""
+    c = x.shape[1]
+    bs = (1, c) + (1,) * (x.ndim - 2)
+    mean = np.asarray(truth["mean"], np.float64).reshape(bs)
+    r = 1.0 / np.sqrt(np.asarray(truth["var"], np.float64)).reshape(bs)
+    g = np.ones(c) if gamma is None else gamma.astype(np.float64)
+    b = np.zeros(c) if (gamma is None or beta is None) else beta.astype(np.float64)
+    ybn = (x.astype(np.float64) - mean) * r * g.reshape(bs) + b.reshape(bs)
+    return np.abs(ybn) < tol
+
+
+def check_layer(got, truth, x, gamma, beta, what=""):
+    """Compares one layer's outputs (dict of numpy arrays) with an oracle's."""
+    skip = borderline(truth, x, gamma, beta)
+    assert x.size < 10000 or skip.mean() < 1e-3
+    for k in ("mean", "var", "run_mean", "run_var"):
+        if got.get(k) is not None and truth.get(k) is not None:
+            assert_close(got[k], truth[k], what + k)
+    assert_close(got["y"], truth["y"], what + "y", skip=skip)
+    assert_close(got["dx"], truth["dx"], what + "dx", skip=skip)
+    if gamma is not None:
+        assert_sum_close(got["dgamma"], truth["dgamma"], what + "dgamma")
+        assert_sum_close(got["dbeta"], truth["dbeta"], what + "dbeta")
