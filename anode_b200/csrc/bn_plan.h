@@ -44,7 +44,7 @@ struct Plan {
   uint32_t total_tiles;     // units * tiles_per_unit
   uint32_t grid;            // thread blocks launched
   uint32_t lookahead_steps; // distance, in steps, between reducing and applying a tile
-  uint32_t div_mul;         // floor(2^32 / (piece_len/vec)) + 1, see fast_div
+  uint32_t div_mul;         // floor(2^32 / (piece_len/vec)) + 1, see fast_div; 0 when piece_len/vec == 1
   // workspace offsets, in bytes from the workspace base
   uint32_t off_done, off_ready, off_applied, off_coef, off_local, off_part;
   uint64_t ws_bytes;
@@ -57,10 +57,12 @@ struct TileRange {
   uint64_t base;             // float offset of (n0, c0, col0)
 };
 
-// n / d with mul = floor(2^32/d) + 1.  Exact whenever n <= 65535 and (n/d + 1)*d <= 65536,
-// which holds for a vector index n inside a tile of at most kMaxTileElems elements.
+// n / d with mul = floor(2^32/d) + 1 (d >= 2; mul == 0 stands for d == 1).  Exact whenever
+// n <= 65535 and (n/d + 1)*d <= 65536, which holds for a vector index n inside a tile of at
+// most kMaxTileElems elements.
 ANODE_HD uint32_t fast_div(uint32_t n, uint32_t mul)
 {
+  if (mul == 0) return n;
 #if defined(__CUDA_ARCH__)
   return __umulhi(n, mul);
 #else
@@ -159,7 +161,7 @@ inline Plan make_plan(uint32_t dim0, uint32_t C, uint32_t N, bool aligned16,
   // wait for the unit free of cycles; the slack steps give its completion time to land.
   p.lookahead_steps = ceil_div_u32(p.tiles_per_unit, p.grid) + slack_steps;
   const uint32_t per_row = p.piece_len / p.vec ? p.piece_len / p.vec : 1;
-  p.div_mul = (uint32_t)((1ull << 32) / per_row) + 1;
+  p.div_mul = per_row > 1 ? (uint32_t)((1ull << 32) / per_row) + 1 : 0;   // 0: divide by one
 
   uint64_t off = 256;                                     // header: status word and padding
   p.off_done = (uint32_t)off;    off = align_up_u64(off + 4ull * p.units, 256);

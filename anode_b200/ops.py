@@ -375,11 +375,28 @@ class FusedBatchNormRelu:
         self._ws = None
         self._x = None
 
+    launches_per_step = 2      # one forward kernel, one backward kernel
+
     def _workspace(self, x):
         key = dims_of(x)
         if self._ws is None or self._ws.key != key:
             self._ws = Workspace(*key, x.device)
         return self._ws
+
+    def status(self):
+        """Device status word of the last launches (0 = clean); synchronises the stream."""
+        return 0 if self._ws is None else self._ws.status()
+
+    def step_from_host(self, hx, hdy, hy, hdx, x, dy, y, dx):
+        """One forward + backward with the tensors in (pinned) host memory: copies x and dy to
+        the device buffers, runs both kernels, copies y and dx back.  Everything is enqueued on
+        the current stream; the caller synchronises."""
+        x.copy_(hx, non_blocking=True)
+        dy.copy_(hdy, non_blocking=True)
+        self.forward(x, out=y)
+        self.backward(dy, out=dx)
+        hy.copy_(y, non_blocking=True)
+        hdx.copy_(dx, non_blocking=True)
 
     def forward(self, x, out=None):
         axes = list(range(x.dim() - 2))

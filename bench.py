@@ -1,0 +1,394 @@
+#!/usr/bin/env python
+"""Benchmark of the batch-norm + ReLU hot path: forward + backward elements/s.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+
+A step is one fused forward and one fused backward over one batch of synthetic input.
+Default workload: the sync-BN configuration of the reference benchmark definition
+(global x f32 [2048, 256, 56, 56], sharded by batch over the N GPUs; fixed global batch, so
+scaling is "strong").  Prints ONE JSON line on rank 0.  For N > 1 launch under torchrun.
+
+Fields beyond the common contract:
+  roofline      dominant kernel (backward, 12 algorithmic bytes/element) against the measured
+                HBM copy peak of MEASURED_PEAKS.json (fallback 6650 GB/s)
+  roofline_fwd, roofline_step   same for the forward kernel (8 B/el) and the whole step (20 B/el)
+  e2e           same metric with inputs in pinned HOST memory: H2D of x, dy and D2H of y, dx inside
+                the timed region, through the public host-buffer call of anode_b200.ops
+  cpu_baseline  the CPU restatement of the reference's kernel chain (oracle/, OpenMP, all host
+                cores) timed on a bounded channel subset of the same workload
+  other_workloads  (N=1 only) the remaining single-GPU shapes of the benchmark definition
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+BYTES_FWD, BYTES_BWD = 8.0, 12.0     # read x, write y | read x, read dy, write dx
+
+WORKLOADS = {
+    # name: global shape, distribution, loc, scale, sharded axis
+    "cfg2_stem": dict(shape=(256, 64, 112, 112), dist="normal", loc=0.5, scale=2.0, axis=0),
+    "cfg3_syncbn": dict(shape=(2048, 256, 56, 56), dist="normal", loc=0.0, scale=1.0, axis=0),
+    "cfg4_unet3d": dict(shape=(4, 32, 128, 128, 128), dist="normal", loc=0.0, scale=1.0, axis=2),
+    "cfg5_wide": dict(shape=(1024, 2048, 7, 7), dist="student3", loc=0.0, scale=4.0, axis=0),
+}
+DEFAULT = "cfg3_syncbn"
+SEED = 20240607
+BLOCKS = 8        # the global tensor is generated in 8 blocks along the sharded axis, whatever N is
+
+
+def hbm_peak():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+def local_shape(w, rank, world):
+    shape = list(w["shape"])
+    assert shape[w["axis"]] % BLOCKS == 0 and BLOCKS % world == 0
+    shape[w["axis"]] //= world
+    return tuple(shape)
+
+
+def gen_local(w, rank, world, device):
+    """This rank's shard of the seeded global tensor (identical global data for every N)."""
+    import torch
+    ax = w["axis"]
+    bshape = list(w["shape"]); bshape[ax] //= BLOCKS
+    per = BLOCKS // world
+    xs, dys = [], []
+    for b in range(rank * per, (rank + 1) * per):
+        g = torch.Generator(device=device); g.manual_seed(SEED + 1000 * b)
+        if w["dist"] == "normal":
+            x = torch.randn(bshape, device=device, generator=g) * w["scale"] + w["loc"]
+        else:   # scale * Student-t(3) = Z / sqrt(chi2_3 / 3)
+            z = torch.randn(bshape, device=device, generator=g)
+            chi = torch.zeros(bshape, device=device)
+            for _ in range(3):
+                chi += torch.randn(bshape, device=device, generator=g) ** 2
+            x = z * torch.rsqrt(chi / 3.0) * w["scale"]
+            del z, chi
+        xs.append(x)
+        dys.append(torch.randn(bshape, device=device, generator=g))
+    x = torch.cat(xs, dim=ax).contiguous() if len(xs) > 1 else xs[0]
+    dy = torch.cat(dys, dim=ax).contiguous() if len(dys) > 1 else dys[0]
+    c = w["shape"][1]
+    g = torch.Generator(device=device); g.manual_seed(SEED - 1)
+    gamma = torch.rand(c, device=device, generator=g) + 0.5
+    beta = torch.rand(c, device=device, generator=g) * 0.2 - 0.1
+    return x, dy, gamma, beta
+
+
+class ClockSampler:
+    """nvidia-smi in the background while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.p = index, None
+
+    def start(self):
+        try:
+            self.p = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q,
+                                       "--format=csv,noheader,nounits", "-lms", "100"],
+                                      stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except Exception:
+            self.p = None
+
+    def stop(self):
+        if self.p is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.p.terminate()
+        try:
+            out, _ = self.p.communicate(timeout=5)
+        except Exception:
+            self.p.kill(); out = ""
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.splitlines():
+            f = [s.strip() for s in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for n, v in zip(names, f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def cpu_baseline(w, seconds_hint=15.0):
+    """Times the CPU restatement of the reference's kernel chain on a channel subset."""
+    import numpy as np
+    from oracle import bn_oracle as o
+    shape = list(w["shape"])
+    c_sub = 16 if shape[1] >= 16 else shape[1]
+    per_channel = 1
+    for i, s in enumerate(shape):
+        if i != 1:
+            per_channel *= s
+    while c_sub > 1 and c_sub * per_channel > 120e6:
+        c_sub //= 2
+    shape[1] = c_sub
+    rng = np.random.default_rng(SEED)
+    x = rng.standard_normal(shape, dtype=np.float32) * np.float32(w["scale"]) + np.float32(w["loc"])
+    dy = rng.standard_normal(shape, dtype=np.float32)
+    g = rng.uniform(0.5, 1.5, c_sub).astype(np.float32); b = rng.uniform(-0.1, 0.1, c_sub).astype(np.float32)
+    rm, rv = np.zeros(c_sub, np.float32), np.ones(c_sub, np.float32)
+    times = []
+    t_all = time.perf_counter()
+    for _ in range(3):
+        t0 = time.perf_counter()
+        o.bn_relu_fwd_bwd_f32(x, dy, 1e-5, 0.1, rm, rv, g, b, block_sz=0)
+        times.append(time.perf_counter() - t0)
+        if time.perf_counter() - t_all > seconds_hint:
+            break
+    best = min(times)
+    return {"value": x.size / best, "unit": "elements/s", "cores": o.num_threads(), "kind": "port",
+            "sample": "%d of %d channels of %s, %d elements, best of %d runs, f32, 11 passes as the "
+                      "reference's kernel chain" % (c_sub, w["shape"][1], "x".join(map(str, w["shape"])), x.size, len(times)),
+            "seconds": best}, times
+
+
+def run_reference(args, rank):
+    """--impl reference: the reference has no CPU batch-norm; its kernel chain restated in C
+    (oracle/, OpenMP over all host cores) is timed.  When a GPU is visible the reference's own
+    CUDA kernels (oracle/_ref, compiled unmodified) are timed beside it as extra information."""
+    if rank != 0:
+        return
+    w = WORKLOADS[args.workload]
+    base, times = cpu_baseline(w, seconds_hint=60.0)
+    # honour --steps/--warmup on the bounded sample
+    import numpy as np
+    from oracle import bn_oracle as o
+    line = {
+        "impl": "reference", "metric": "bn_relu_fwd_bwd_elements_per_s", "value": base["value"], "unit": "elements/s",
+        "n_gpus": args.gpus, "steps": len(times), "warmup": 0, "ms_per_step": 1e3 * base["seconds"],
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": args.workload + " (CPU: bounded channel subset)", "global_shape": list(w["shape"])},
+        "cpu_baseline": base,
+        "e2e": {"value": base["value"], "unit": "elements/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    try:
+        import torch
+        from oracle import ref_gpu
+        if torch.cuda.is_available() and ref_gpu.available():
+            torch.cuda.set_device(0)
+            x, dy, _, _ = gen_local(w, 0, 1, torch.device("cuda", 0))
+            c = x.shape[1]
+            rm = torch.zeros(c, device="cuda"); rv = torch.ones(c, device="cuda")
+            ts = []
+            for i in range(3):
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                ref_gpu.bn_relu_fwd_bwd(x, dy, 1e-5, 0.1, rm, rv, timing=(e0, e1))
+                torch.cuda.synchronize()
+                ts.append(e0.elapsed_time(e1))
+            ms = min(ts[1:])
+            line["ref_gpu_kernels"] = {
+                "what": "the reference's own 11 CUDA kernels (oracle/_ref, built for sm_100, block_sz=1024, "
+                        "max_block_ct=32*SMs) on this GPU, whole workload on one GPU",
+                "ms_per_step": ms, "value": x.numel() / (ms * 1e-3), "unit": "elements/s"}
+    except Exception as e:     # extra information only
+        line["ref_gpu_kernels"] = {"unavailable": repr(e)[:200]}
+    print(json.dumps(line), flush=True)
+
+
+def time_layer(layer, x, dy, y, dx, steps, warmup, dist, sampler=None):
+    """W warm-up steps, then K timed steps bracketed by barrier + synchronize; device time by CUDA
+    events on the launching stream; per-kernel events inside.  Returns (total_ms, fwd_ms, bwd_ms)."""
+    import torch
+    for _ in range(warmup):
+        layer.forward(x, out=y); layer.backward(dy, out=dx)
+    torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier()
+    torch.cuda.synchronize()
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(steps)]
+    if sampler:
+        sampler.start()
+    for i in range(steps):
+        ev[i][0].record()
+        layer.forward(x, out=y)
+        ev[i][1].record()
+        layer.backward(dy, out=dx)
+        ev[i][2].record()
+    torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier()
+    torch.cuda.synchronize()
+    clocks = sampler.stop() if sampler else None
+    total = ev[0][0].elapsed_time(ev[-1][2])
+    fwd = sum(e[0].elapsed_time(e[1]) for e in ev) / steps
+    bwd = sum(e[1].elapsed_time(e[2]) for e in ev) / steps
+    return total, fwd, bwd, clocks
+
+
+def make_layer(ops, channels, world, gamma, beta):
+    if world == 1:
+        layer = ops.FusedBatchNormRelu(channels, epsilon=1e-5, avg_rate=0.1, affine=True, relu=True)
+    else:
+        layer = ops.SyncBatchNormRelu(channels, epsilon=1e-5, avg_rate=0.1, affine=True, relu=True)
+    layer.gamma.copy_(gamma); layer.beta.copy_(beta)
+    return layer
+
+
+def bench_workload(ops, name, rank, world, steps, warmup, dist, device, sample_clocks, with_e2e):
+    import torch
+    w = WORKLOADS[name]
+    x, dy, gamma, beta = gen_local(w, rank, world, device)
+    y = torch.empty_like(x); dx = torch.empty_like(x)
+    layer = make_layer(ops, x.shape[1], world, gamma, beta)
+    sampler = ClockSampler(device.index) if (sample_clocks and rank == 0) else None
+    total, fwd, bwd, clocks = time_layer(layer, x, dy, y, dx, steps, warmup, dist, sampler)
+    status = layer.status()
+    t = torch.tensor([total, fwd, bwd, float(status)], dtype=torch.float64, device=device)
+    if dist is not None:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    total, fwd, bwd, status = [float(v) for v in t.tolist()]
+    if status != 0:
+        raise RuntimeError("device status word %d after the timed region" % int(status))
+    n_local = x.numel()
+    n_global = n_local * world
+    ms = total / steps
+    res = {"ms_per_step": ms, "fwd_ms": fwd, "bwd_ms": bwd, "elements_local": n_local, "elements_global": n_global,
+           "value": n_global / (ms * 1e-3), "clocks": clocks, "launches_per_step": layer.launches_per_step}
+    if with_e2e:
+        res["e2e"] = bench_e2e(ops, layer, x, dy, y, dx, dist, device, min(steps, 3))
+    return res
+
+
+def bench_e2e(ops, layer, x, dy, y, dx, dist, device, steps):
+    """Same metric through the host-buffer call: pinned host x, dy in; y, dx back out."""
+    import torch
+    hx = torch.empty(x.shape, dtype=torch.float32, pin_memory=True); hx.copy_(x)
+    hdy = torch.empty(x.shape, dtype=torch.float32, pin_memory=True); hdy.copy_(dy)
+    hy = torch.empty(x.shape, dtype=torch.float32, pin_memory=True)
+    hdx = torch.empty(x.shape, dtype=torch.float32, pin_memory=True)
+    layer.step_from_host(hx, hdy, hy, hdx, x, dy, y, dx)      # warm-up
+    torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        layer.step_from_host(hx, hdy, hy, hdx, x, dy, y, dx)
+    e1.record()
+    torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier()
+    ms = torch.tensor([e0.elapsed_time(e1) / steps], dtype=torch.float64, device=device)
+    if dist is not None:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    ms = float(ms.item())
+    world = dist.get_world_size() if dist is not None else 1
+    nbytes = x.numel() * 4
+    return {"value": x.numel() * world / (ms * 1e-3), "unit": "elements/s", "ms_per_step": ms, "steps": steps,
+            "h2d_bytes_per_step": 2 * nbytes, "d2h_bytes_per_step": 2 * nbytes}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default=DEFAULT, choices=sorted(WORKLOADS))
+    ap.add_argument("--no-extras", action="store_true", help="skip cpu_baseline, e2e and other_workloads")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+
+    import torch
+    import torch.distributed as tdist
+    from anode_b200 import ops            # raises if the CUDA library is not built
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device; there is no CPU path")
+    if world != args.gpus:
+        raise SystemExit("--gpus %d but WORLD_SIZE=%d: launch with torchrun --nproc-per-node %d" % (args.gpus, world, args.gpus))
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    dist = None
+    if world > 1:
+        tdist.init_process_group("nccl", device_id=device)
+        dist = tdist
+
+    main_res = bench_workload(ops, args.workload, rank, world, args.steps, args.warmup, dist, device,
+                              sample_clocks=True, with_e2e=not args.no_extras)
+    peak, peak_kind = hbm_peak()
+
+    def roof(bytes_per_el, ms):
+        ach = bytes_per_el * main_res["elements_local"] / (ms * 1e-3) / 1e9
+        return {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak,
+                "peak_kind": peak_kind, "traffic": None}
+
+    w = WORKLOADS[args.workload]
+    line = {
+        "metric": "bn_relu_fwd_bwd_elements_per_s", "value": main_res["value"], "unit": "elements/s",
+        "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": main_res["ms_per_step"],
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": args.workload, "global_shape": list(w["shape"]), "local_shape": list(local_shape(w, rank, world)),
+                   "sharded_axis": w["axis"], "layout": "NCHW f32, eps=1e-5, avg_rate=0.1, gamma/beta, ReLU",
+                   "l2": "inputs larger than L2 (no flush needed)" if main_res["elements_local"] * 4 > 512e6 else "inputs near L2 size",
+                   "parallelism": "syncbn_dp%d" % world},
+        "per_gpu_value": main_res["value"] / world,
+        "fwd_ms": main_res["fwd_ms"], "bwd_ms": main_res["bwd_ms"],
+        "roofline": dict(roof(BYTES_BWD, main_res["bwd_ms"]), kernel="bn_pipeline_kernel<bwd>"),
+        "roofline_fwd": dict(roof(BYTES_FWD, main_res["fwd_ms"]), kernel="bn_pipeline_kernel<fwd>"),
+        "roofline_step": roof(BYTES_FWD + BYTES_BWD, main_res["ms_per_step"]),
+        "clocks": main_res["clocks"],
+        "gpu_launches": main_res["launches_per_step"] * args.steps,
+    }
+    if "e2e" in main_res:
+        line["e2e"] = main_res["e2e"]
+    try:
+        with open(os.path.join(ROOT, "profiles", "traffic.json")) as f:
+            tr = json.load(f).get(args.workload if world == 1 else "", {})
+        for key, rk in (("bwd", "roofline"), ("fwd", "roofline_fwd")):
+            if key in tr:
+                line[rk]["traffic"] = tr[key]["bytes_per_element"] * main_res["elements_local"]
+                line[rk]["traffic_source"] = tr[key]["source"]
+    except Exception:
+        pass
+
+    if world == 1 and not args.no_extras:
+        others = {}
+        for name in sorted(WORKLOADS):
+            if name == args.workload:
+                continue
+            torch.cuda.empty_cache()
+            r = bench_workload(ops, name, 0, 1, max(5, args.steps // 2), 3, None, device, False, False)
+            others[name] = {"value": r["value"], "ms_per_step": r["ms_per_step"], "fwd_ms": r["fwd_ms"], "bwd_ms": r["bwd_ms"],
+                            "step_frac_of_hbm_peak": 20.0 * r["elements_local"] / (r["ms_per_step"] * 1e-3) / 1e9 / peak}
+        line["other_workloads"] = others
+        if rank == 0:
+            torch.cuda.empty_cache()
+            line["cpu_baseline"], _ = cpu_baseline(w)
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -67,13 +67,19 @@ def test_benchmark_shapes_pick_the_expected_regimes():
     assert plan(49, 3, 5)["vec"] == 1                                                    # nothing aligns: scalar
 
 
+def test_division_by_one_is_special_cased():
+    assert plan(1, 2, 3, aligned=False)["div_mul"] == 0
+    assert plan(784, 64, 32)["div_mul"] == (1 << 32) // 196 + 1
+
+
 def test_fast_division_is_exact_in_its_domain():
     # q = (n * mul) >> 32 with mul = floor(2^32/d) + 1 must equal n // d for every vector index of a
     # tile: n < rows*d <= 65532
     rng = np.random.default_rng(0)
-    ds = np.unique(np.concatenate([np.arange(1, 300), rng.integers(300, 65532, 400), [16383, 32766, 65532]]))
+    ds = np.unique(np.concatenate([np.arange(2, 300), rng.integers(300, 65532, 400), [16383, 32766, 65532]]))
     for d in ds:
         mul = (1 << 32) // int(d) + 1
+        assert mul < (1 << 32)          # fits the plan's 32-bit field (d == 1 is special-cased)
         rows = 65532 // int(d)
         n = np.arange(0, rows * int(d), dtype=np.uint64)
         if n.size > 20000:
