@@ -36,6 +36,22 @@ __device__ __forceinline__ void st_release_sys(uint32_t *p, uint32_t v)
   asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
+// ---- L2 eviction policies ----------------------------------------------------------------
+// keep: data that will be read a second time (the reduce pass of a tile);
+// drop: data that is dead after this access (the apply pass's re-read, and every output).
+__device__ __forceinline__ uint64_t policy_keep()
+{
+  uint64_t p;
+  asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
+  return p;
+}
+__device__ __forceinline__ uint64_t policy_drop()
+{
+  uint64_t p;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+  return p;
+}
+
 // ---- packs of VEC floats ----------------------------------------------------------------
 template <int VEC> struct Pack;
 template <> struct Pack<4> {
@@ -45,16 +61,38 @@ template <> struct Pack<4> {
     const float4 t = *reinterpret_cast<const float4 *>(p);
     Pack r; r.v[0] = t.x; r.v[1] = t.y; r.v[2] = t.z; r.v[3] = t.w; return r;
   }
+  __device__ __forceinline__ static Pack load(const float *p, uint64_t pol)
+  {
+    Pack r;
+    asm volatile("ld.global.L2::cache_hint.v4.f32 {%0, %1, %2, %3}, [%4], %5;"
+                 : "=f"(r.v[0]), "=f"(r.v[1]), "=f"(r.v[2]), "=f"(r.v[3]) : "l"(p), "l"(pol));
+    return r;
+  }
   // streaming store: the written tensor is not read again by this kernel
   __device__ __forceinline__ void store_stream(float *p) const
   {
     __stcs(reinterpret_cast<float4 *>(p), make_float4(v[0], v[1], v[2], v[3]));
   }
+  __device__ __forceinline__ void store(float *p, uint64_t pol) const
+  {
+    asm volatile("st.global.L2::cache_hint.v4.f32 [%0], {%1, %2, %3, %4}, %5;"
+                 ::"l"(p), "f"(v[0]), "f"(v[1]), "f"(v[2]), "f"(v[3]), "l"(pol) : "memory");
+  }
 };
 template <> struct Pack<1> {
   float v[1];
   __device__ __forceinline__ static Pack load(const float *p) { Pack r; r.v[0] = *p; return r; }
+  __device__ __forceinline__ static Pack load(const float *p, uint64_t pol)
+  {
+    Pack r;
+    asm volatile("ld.global.L2::cache_hint.f32 %0, [%1], %2;" : "=f"(r.v[0]) : "l"(p), "l"(pol));
+    return r;
+  }
   __device__ __forceinline__ void store_stream(float *p) const { __stcs(p, v[0]); }
+  __device__ __forceinline__ void store(float *p, uint64_t pol) const
+  {
+    asm volatile("st.global.L2::cache_hint.f32 [%0], %1, %2;" ::"l"(p), "f"(v[0]), "l"(pol) : "memory");
+  }
 };
 template <int VEC> __device__ __forceinline__ Pack<VEC> pack_fill(float f)
 {

@@ -16,7 +16,7 @@ static uint32_t env_u32(const char *name, uint32_t dflt)
 const Tunables &tunables()
 {
   static const Tunables t = {
-      env_u32("ANODE_B200_TILE_FLOATS", 8192),
+      env_u32("ANODE_B200_TILE_FLOATS", 32768),
       env_u32("ANODE_B200_SLACK_STEPS", 1),
       env_u32("ANODE_B200_BLOCKS_PER_SM", 4),
   };

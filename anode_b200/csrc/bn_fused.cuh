@@ -202,6 +202,7 @@ __device__ __forceinline__ void reduce_fwd_R(const FusedArgs &a, const TileRange
   const uint32_t mul = a.plan.div_mul;
   // Shifted sums: K is this thread's first element, so s and q stay small and q - s^2/n
   // does not cancel catastrophically whatever the channel mean is.
+  const uint64_t keep = policy_keep();
   float K = 0.f;
   if (tid < nvec) K = a.x[vec_off<VEC>(tr, per_row, mul, rs, tid)];
   float s = 0.f, q = 0.f;
@@ -210,7 +211,7 @@ __device__ __forceinline__ void reduce_fwd_R(const FusedArgs &a, const TileRange
 #pragma unroll
     for (int u = 0; u < kUnroll; ++u) {
       const uint32_t j = j0 + u * kThreads;
-      if (j < nvec) v[u] = Pack<VEC>::load(a.x + vec_off<VEC>(tr, per_row, mul, rs, j));
+      if (j < nvec) v[u] = Pack<VEC>::load(a.x + vec_off<VEC>(tr, per_row, mul, rs, j), keep);
       else v[u] = pack_fill<VEC>(K);
     }
 #pragma unroll
@@ -239,6 +240,7 @@ __device__ __forceinline__ void apply_fwd_R(const FusedArgs &a, const TileRange 
   const float4 cf = __ldcg(ws_f4(a, a.plan.off_coef) + 2 * (size_t)tr.c0);
   const float mean = cf.x, scale = cf.y, beta = cf.z;
   const bool relu = a.relu != 0;
+  const uint64_t drop = policy_drop();
   for (uint32_t j0 = tid; j0 < nvec; j0 += kThreads * kUnroll) {
     Pack<VEC> v[kUnroll];
     size_t off[kUnroll];
@@ -246,7 +248,7 @@ __device__ __forceinline__ void apply_fwd_R(const FusedArgs &a, const TileRange 
     for (int u = 0; u < kUnroll; ++u) {
       const uint32_t j = j0 + u * kThreads;
       off[u] = vec_off<VEC>(tr, per_row, mul, rs, j < nvec ? j : 0);
-      if (j < nvec) v[u] = Pack<VEC>::load(a.x + off[u]);
+      if (j < nvec) v[u] = Pack<VEC>::load(a.x + off[u], drop);
     }
 #pragma unroll
     for (int u = 0; u < kUnroll; ++u) {
@@ -257,7 +259,7 @@ __device__ __forceinline__ void apply_fwd_R(const FusedArgs &a, const TileRange 
           const float yb = fmaf(v[u].v[i] - mean, scale, beta);
           v[u].v[i] = relu ? positive_clip(yb) : yb;
         }
-        v[u].store_stream(a.out + off[u]);
+        v[u].store(a.out + off[u], drop);
       }
     }
   }
@@ -276,6 +278,7 @@ __device__ __forceinline__ void reduce_bwd_R(const FusedArgs &a, const TileRange
   const float beta = (a.gamma && a.beta) ? a.beta[c] : 0.0f;
   const float scale = g * inv_std(a.var_in[c]);
   const bool relu = a.relu != 0;
+  const uint64_t keep = policy_keep();
   float s1 = 0.f, s2 = 0.f;
   for (uint32_t j0 = tid; j0 < nvec; j0 += kThreads * kUnroll) {
     Pack<VEC> vx[kUnroll], vd[kUnroll];
@@ -284,8 +287,8 @@ __device__ __forceinline__ void reduce_bwd_R(const FusedArgs &a, const TileRange
       const uint32_t j = j0 + u * kThreads;
       if (j < nvec) {
         const size_t off = vec_off<VEC>(tr, per_row, mul, rs, j);
-        vx[u] = Pack<VEC>::load(a.x + off);
-        vd[u] = Pack<VEC>::load(a.dy + off);
+        vx[u] = Pack<VEC>::load(a.x + off, keep);
+        vd[u] = Pack<VEC>::load(a.dy + off, keep);
       } else {
         vx[u] = pack_fill<VEC>(mean);
         vd[u] = pack_fill<VEC>(0.f);
@@ -317,6 +320,7 @@ __device__ __forceinline__ void apply_bwd_R(const FusedArgs &a, const TileRange 
   const float4 c1 = __ldcg(ws_f4(a, a.plan.off_coef) + 2 * (size_t)tr.c0 + 1);
   const float mean = c0.x, scale = c0.y, beta = c0.z, cB = c1.x, cC = c1.y;
   const bool relu = a.relu != 0, acc = a.accumulate != 0;
+  const uint64_t drop = policy_drop();
   for (uint32_t j0 = tid; j0 < nvec; j0 += kThreads * kUnroll) {
     Pack<VEC> vx[kUnroll], vd[kUnroll];
     size_t off[kUnroll];
@@ -324,7 +328,7 @@ __device__ __forceinline__ void apply_bwd_R(const FusedArgs &a, const TileRange 
     for (int u = 0; u < kUnroll; ++u) {
       const uint32_t j = j0 + u * kThreads;
       off[u] = vec_off<VEC>(tr, per_row, mul, rs, j < nvec ? j : 0);
-      if (j < nvec) { vx[u] = Pack<VEC>::load(a.x + off[u]); vd[u] = Pack<VEC>::load(a.dy + off[u]); }
+      if (j < nvec) { vx[u] = Pack<VEC>::load(a.x + off[u], drop); vd[u] = Pack<VEC>::load(a.dy + off[u], drop); }
     }
 #pragma unroll
     for (int u = 0; u < kUnroll; ++u) {
@@ -340,7 +344,7 @@ __device__ __forceinline__ void apply_bwd_R(const FusedArgs &a, const TileRange 
           const float dx = fmaf(scale, dz, fmaf(cB, d, cC));
           o.v[i] = acc ? o.v[i] + dx : dx;
         }
-        o.store_stream(a.out + off[u]);
+        o.store(a.out + off[u], drop);
       }
     }
   }

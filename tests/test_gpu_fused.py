@@ -77,7 +77,7 @@ def test_fused_layer_matches_oracle(ops, shape, dist, loc, scale, affine):
         # Conditioning, not the kernel: the mean is returned (and re-read by the backward pass) as
         # f32, so xhat = (x - mean)/sigma carries half an ulp of |mean| divided by sigma, times gamma.
         atol = 1e-5 + 1.5 * float(np.spacing(np.float32(abs(loc)))) / scale
-    check_layer(got, truth, d["x"], d["gamma"], d["beta"], "vs f64 ", atol_elem=atol)
+    check_layer(got, truth, d["x"], d["gamma"], d["beta"], "vs f64 ", atol_elem=atol, check_sums=atol == 1e-5)
     if abs(loc) <= 10 * scale:
         # the literal f32 restatement of the reference's kernel chain (it is itself inaccurate
         # when |mean| >> sigma, so that case is checked against float64 only)

@@ -69,9 +69,10 @@ def borderline(truth, x, gamma, beta, tol=1e-5):
     return np.abs(ybn) < tol
 
 
-def check_layer(got, truth, x, gamma, beta, what="", atol_elem=ATOL):
+def check_layer(got, truth, x, gamma, beta, what="", atol_elem=ATOL, check_sums=True):
     """Compares one layer's outputs (dict of numpy arrays) with an oracle's.  `atol_elem`
-    replaces the absolute tolerance on y and dx for deliberately ill-conditioned inputs."""
+    replaces the absolute tolerance on y and dx for deliberately ill-conditioned inputs, where
+    `check_sums=False` also drops dgamma/dbeta (a single undecidable ReLU mask moves them by |dy|)."""
     skip = borderline(truth, x, gamma, beta, tol=atol_elem)
     assert x.size < 10000 or skip.mean() < 1e-3
     for k in ("mean", "var", "run_mean", "run_var"):
@@ -79,6 +80,6 @@ def check_layer(got, truth, x, gamma, beta, what="", atol_elem=ATOL):
             assert_close(got[k], truth[k], what + k)
     assert_close(got["y"], truth["y"], what + "y", skip=skip, atol=atol_elem)
     assert_close(got["dx"], truth["dx"], what + "dx", skip=skip, atol=atol_elem)
-    if gamma is not None:
+    if gamma is not None and check_sums:
         assert_sum_close(got["dgamma"], truth["dgamma"], what + "dgamma")
         assert_sum_close(got["dbeta"], truth["dbeta"], what + "dbeta")
