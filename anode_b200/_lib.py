@@ -7,7 +7,8 @@ import ctypes
 import os
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "libanode_routines_gpu.so")
+# ANODE_B200_LIB selects another build of the same library (e.g. an instrumented one)
+LIB_PATH = os.environ.get("ANODE_B200_LIB") or os.path.join(HERE, "libanode_routines_gpu.so")
 
 u32, f32, c_int = ctypes.c_uint32, ctypes.c_float, ctypes.c_int
 vp, size_t = ctypes.c_void_p, ctypes.c_size_t

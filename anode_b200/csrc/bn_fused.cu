@@ -1,6 +1,7 @@
 // Host side of the fused batch-norm (+ReLU) entry points: argument checks, the tile plan,
 // and the cooperative launch of the persistent kernels of bn_fused.cuh.
 #include "bn_host.h"
+#include "bn_ring.cuh"
 
 namespace anode_b200 {
 
@@ -10,15 +11,20 @@ static uint32_t env_u32(const char *name, uint32_t dflt)
   const char *s = getenv(name);
   if (!s || !*s) return dflt;
   const long v = strtol(s, nullptr, 10);
-  return v > 0 ? (uint32_t)v : dflt;
+  return v >= 0 ? (uint32_t)v : dflt;
 }
 
 const Tunables &tunables()
 {
   static const Tunables t = {
       env_u32("ANODE_B200_TILE_FLOATS", 32768),
-      env_u32("ANODE_B200_SLACK_STEPS", 1),
+      env_u32("ANODE_B200_SLACK_STEPS", 3),
       env_u32("ANODE_B200_BLOCKS_PER_SM", 4),
+      env_u32("ANODE_B200_RING", 1),
+      env_u32("ANODE_B200_RING_SLOTS", 3),
+      env_u32("ANODE_B200_RING_FLOATS_FWD", 16384),
+      env_u32("ANODE_B200_RING_FLOATS_BWD", 8192),
+      env_u32("ANODE_B200_RING_BLOCKS_PER_SM", 1),
   };
   return t;
 }
@@ -44,7 +50,104 @@ uint32_t sm_count()
 Plan plan_for(uint32_t dim0, uint32_t C, uint32_t N, bool aligned16)
 {
   const Tunables &t = tunables();
-  return make_plan(dim0, C, N, aligned16, sm_count() * t.blocks_per_sm, t.tile_floats, t.slack_steps);
+  return make_plan(dim0, C, N, aligned16, sm_count() * t.blocks_per_sm, t.tile_floats, 1);
+}
+
+// Shared-memory layout of the warp-specialised kernel for plan `p` (see bn_ring.cuh).
+static RingGeom ring_geom(const Plan &p, int dir, uint32_t slots, uint32_t slot_floats)
+{
+  RingGeom g{};
+  g.slots = slots; g.slot_floats = slot_floats;
+  uint32_t off = (uint32_t)align_up_u64(sizeof(RingCtl), 128);
+  g.res_stride = p.cb > kConsumers / 32 ? p.cb : kConsumers / 32;   // regime R: one partial per consumer warp
+  g.off_res = off;  off += (uint32_t)align_up_u64((uint64_t)kResQ * g.res_stride * 16, 128);
+  g.off_coef = off; off += (uint32_t)align_up_u64((uint64_t)kCoefQ * p.cb * 32, 128);
+  g.off_seg = off;  if (p.regime == 1) off += 2 * kSegMaxFloats * 4;
+  g.off_slots = off;
+  g.slot_stride = (uint32_t)align_up_u64((uint64_t)slot_floats * 4 * (dir == 1 ? 2 : 1) + (dir == 1 ? (uint64_t)p.cb * 16 : 0), 128);
+  g.smem_bytes = off + slots * g.slot_stride;
+  return g;
+}
+
+// Plan for the warp-specialised kernel, or false when it does not apply (scalar paths, tiles that
+// do not fit a slot, too little shared memory): the caller then uses the plain kernel.
+bool ring_plan_for(uint32_t dim0, uint32_t C, uint32_t N, bool aligned, int dir, Plan &p, RingGeom &g)
+{
+  const Tunables &t = tunables();
+  if (!t.ring || !aligned) return false;
+  uint32_t slot_floats = dir == 0 ? t.ring_floats_fwd : t.ring_floats_bwd;
+  slot_floats = (slot_floats / 4) * 4;
+  if (slot_floats < kSegMaxFloats) slot_floats = kSegMaxFloats;   // a regime-S segment must fit
+  uint32_t slots = t.ring_slots < 2 ? 2 : (t.ring_slots > kMaxSlots ? kMaxSlots : t.ring_slots);
+  uint32_t bps = t.ring_blocks_per_sm ? t.ring_blocks_per_sm : 1;
+  p = make_plan(dim0, C, N, true, sm_count() * bps, slot_floats, t.slack_steps);
+  // regime S (short rows) stays on the plain kernel: its per-unit merge is too slow in one warp
+  if (p.vec != 4 || p.regime != 0) return false;
+  // a tile must fit one slot: rows * len <= slot_floats
+  const uint64_t tile_max = (uint64_t)p.rows_per_tile * p.piece_len;
+  if (tile_max > slot_floats) return false;
+  g = ring_geom(p, dir, slots, slot_floats);
+  const uint32_t budget = 227u * 1024u;
+  while (g.smem_bytes > budget && slots > 2) { --slots; g = ring_geom(p, dir, slots, slot_floats); }
+  if (g.smem_bytes > budget) return false;
+  return true;
+}
+
+typedef void (*RingKernel)(const FusedArgs, const RingGeom);
+
+static RingKernel pick_ring_kernel(const Plan &p, int dir)
+{
+  if (p.regime == 1) return dir == 0 ? bn_ring_kernel<0, 1> : bn_ring_kernel<1, 1>;
+  return dir == 0 ? bn_ring_kernel<0, 0> : bn_ring_kernel<1, 0>;
+}
+
+int launch_ring(FusedArgs &a, const RingGeom &g, int dir, cudaStream_t stream)
+{
+  RingKernel k = pick_ring_kernel(a.plan, dir);
+  static std::mutex mu;
+  static std::map<std::pair<const void *, uint32_t>, int> occ;     // (kernel, smem) -> blocks per SM
+  int per_sm = 0;
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    const auto key = std::make_pair((const void *)k, g.smem_bytes);
+    auto it = occ.find(key);
+    if (it == occ.end()) {
+      if (cudaFuncSetAttribute((const void *)k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(227 * 1024)) != cudaSuccess ||
+          cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, k, (int)kRingThreads, g.smem_bytes) != cudaSuccess) {
+        (void)cudaGetLastError();
+        per_sm = 0;
+      }
+      occ[key] = per_sm;
+    } else {
+      per_sm = it->second;
+    }
+  }
+  const uint32_t fit = (uint32_t)per_sm * sm_count();
+  if (fit == 0) return ANODE_E_LAUNCH;
+  if (a.plan.grid > fit) {
+    a.plan.grid = fit;
+    a.plan.lookahead_steps = ceil_div_u32(a.plan.tiles_per_unit, a.plan.grid) + tunables().slack_steps;
+  }
+  a.use_rec = a.mode == MODE_FUSED ? 1u : 0u;
+  void *params[] = {(void *)&a, (void *)&g};
+  cudaError_t e;
+  if (a.mode == MODE_FUSED)
+    e = cudaLaunchCooperativeKernel((const void *)k, dim3(a.plan.grid), dim3(kRingThreads), params, g.smem_bytes, stream);
+  else
+    e = cudaLaunchKernel((const void *)k, dim3(a.plan.grid), dim3(kRingThreads), params, g.smem_bytes, stream);
+  if (e != cudaSuccess) { (void)cudaGetLastError(); return ANODE_E_LAUNCH; }
+  return ANODE_OK;
+}
+
+// Launches direction `dir` of a prepared call with the best kernel that applies.
+int launch_best(FusedArgs &a, int dir, bool aligned, cudaStream_t stream)
+{
+  Plan rp; RingGeom g;
+  if (ring_plan_for(a.plan.dim0, a.plan.C, a.plan.N, aligned, dir, rp, g) && rp.ws_bytes <= a.ws_capacity) {
+    a.plan = rp;
+    return launch_ring(a, g, dir, stream);
+  }
+  return launch_pipeline(a, dir, stream);
 }
 
 int check_dims(uint32_t dim0, uint32_t dim1, uint32_t dim2)
@@ -86,7 +189,7 @@ int launch_pipeline(FusedArgs &a, int dir, cudaStream_t stream)
   if (a.plan.grid > fit) {
     // fewer blocks are resident than planned: shrink the grid and re-derive the lookahead
     a.plan.grid = fit;
-    a.plan.lookahead_steps = ceil_div_u32(a.plan.tiles_per_unit, a.plan.grid) + tunables().slack_steps;
+    a.plan.lookahead_steps = ceil_div_u32(a.plan.tiles_per_unit, a.plan.grid) + 1;
   }
   void *params[] = {(void *)&a};
   cudaError_t e;
@@ -116,6 +219,7 @@ int prepare_fwd(FusedArgs &a, uint32_t dim0, uint32_t dim1, uint32_t dim2, float
   a = FusedArgs{};
   a.plan = plan_for(dim0, dim1, dim2, aligned16(x) && aligned16(y));
   if (ws_bytes < a.plan.ws_bytes) return ANODE_E_WORKSPACE;
+  a.ws_capacity = ws_bytes;
   a.x = x; a.gamma = gamma; a.beta = beta; a.out = y;
   a.mean = mean; a.var = var; a.run_mean = run_mean; a.run_var = run_var;
   a.ws = static_cast<unsigned char *>(ws);
@@ -137,6 +241,7 @@ int prepare_bwd(FusedArgs &a, uint32_t dim0, uint32_t dim1, uint32_t dim2, int r
   a = FusedArgs{};
   a.plan = plan_for(dim0, dim1, dim2, aligned16(x) && aligned16(dy) && aligned16(dx));
   if (ws_bytes < a.plan.ws_bytes) return ANODE_E_WORKSPACE;
+  a.ws_capacity = ws_bytes;
   a.x = x; a.dy = dy; a.gamma = gamma; a.beta = beta; a.mean_in = mean; a.var_in = var;
   a.out = dx; a.dgamma = dgamma; a.dbeta = dbeta;
   a.ws = static_cast<unsigned char *>(ws);
@@ -163,7 +268,15 @@ extern "C" size_t anode_gpu_batch_norm_fused_workspace_bytes(uint32_t dim0, uint
   if (check_dims(dim0, dim1, dim2)) return 0;
   // the plan depends on pointer alignment, which is not known yet: cover both cases
   const Plan a = plan_for(dim0, dim1, dim2, true), b = plan_for(dim0, dim1, dim2, false);
-  return (size_t)(a.ws_bytes > b.ws_bytes ? a.ws_bytes : b.ws_bytes);
+  uint64_t need = a.ws_bytes > b.ws_bytes ? a.ws_bytes : b.ws_bytes;
+  for (int dir = 0; dir < 2; ++dir) {
+    Plan rp; RingGeom g;
+    if (ring_plan_for(dim0, dim1, dim2, true, dir, rp, g) && rp.ws_bytes > need) need = rp.ws_bytes;
+  }
+#ifdef ANODE_RING_PROFILE
+  need += 1u << 20;     // room for the per-block cycle counters
+#endif
+  return (size_t)need;
 }
 
 extern "C" int anode_gpu_batch_norm_fused_workspace_init(void *workspace, size_t bytes, struct CUstream_st *stream)
@@ -195,7 +308,7 @@ extern "C" int anode_gpu_batch_norm_relu_fused_fwd_3d1_packed_f32(
   const int rc = prepare_fwd(a, dim0, dim1, dim2, epsilon, avg_rate, relu, x, gamma, beta, y, mean, var,
                              run_mean, run_var, workspace, workspace_bytes);
   if (rc) return rc;
-  return launch_pipeline(a, 0, stream);
+  return launch_best(a, 0, aligned16(x) && aligned16(y), stream);
 }
 
 extern "C" int anode_gpu_batch_norm_relu_fused_bwd_3d1_packed_f32(
@@ -209,7 +322,7 @@ extern "C" int anode_gpu_batch_norm_relu_fused_bwd_3d1_packed_f32(
   const int rc = prepare_bwd(a, dim0, dim1, dim2, relu, accumulate, dy, x, mean, var, gamma, beta, dx,
                              dgamma, dbeta, workspace, workspace_bytes);
   if (rc) return rc;
-  return launch_pipeline(a, 1, stream);
+  return launch_best(a, 1, aligned16(x) && aligned16(dy) && aligned16(dx), stream);
 }
 
 extern "C" int anode_gpu_online_average_f32(uint32_t len, float rate, const float *x, float *y,

@@ -36,14 +36,40 @@ struct FusedArgs {
   float *mean, *var, *run_mean, *run_var;   // forward outputs
   float *dgamma, *dbeta;   // backward outputs
   unsigned char *ws;
+  uint64_t ws_capacity;    // bytes the caller provided
   float epsilon, avg_rate;
   uint32_t relu, accumulate, mode;
+  uint32_t use_rec;        // publish tagged records (the warp-specialised kernel reads them)
   double count_total;      // elements per channel over all participating GPUs
 };
 
 // 1/sqrt(v) as every kernel here computes it (IEEE divide and square root), so that the
 // forward pass and the backward pass derive bit-identical scales, hence identical ReLU masks.
-__device__ __forceinline__ float inv_std(float v) { return __fdiv_rn(1.0f, __fsqrt_rn(v)); }
+// The lowest mantissa bit is forced to one: the value can then never have an all-zero bit
+// pattern, which lets a 64-bit (mean, rstd) record double as its own "ready" flag.
+__device__ __forceinline__ float inv_std(float v)
+{
+  return __uint_as_float(__float_as_uint(__fdiv_rn(1.0f, __fsqrt_rn(v))) | 1u);
+}
+
+// Tagged per-channel records in the workspace: zero = not ready; written once per launch with a
+// release store by the thread that completes the channel, read with acquire loads.
+//   forward : (mean, rstd)         rstd has its lowest bit set
+//   backward: (B, C0)              C0 gets its lowest bit set
+__device__ __forceinline__ unsigned long long pack_rec(float lo, float hi)
+{
+  return ((unsigned long long)__float_as_uint(hi) << 32) | (unsigned long long)__float_as_uint(lo);
+}
+__device__ __forceinline__ void st_release_gpu_u64(unsigned long long *p, unsigned long long v)
+{
+  asm volatile("st.release.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ unsigned long long ld_acquire_gpu_u64(const unsigned long long *p)
+{
+  unsigned long long v;
+  asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  return v;
+}
 
 struct SmemCommon {
   float mom[3 * (kThreads / 32)];
@@ -84,15 +110,20 @@ __device__ __forceinline__ void finish_channel_fwd(const FusedArgs &a, uint32_t 
   }
   const float mf = (float)mean;
   const float vf = (float)(m2 / n + (double)a.epsilon);   // biased, epsilon folded in (batch_norm.cu:160)
+  const float r = inv_std(vf);
+  // What other blocks wait for goes out first; the outputs nobody waits for follow.
+  if (a.use_rec) {
+    st_release_gpu_u64(reinterpret_cast<unsigned long long *>(a.ws + a.plan.off_rec) + c, pack_rec(mf, r));
+  } else {
+    const float g = a.gamma ? a.gamma[c] : 1.0f;
+    const float bt = (a.gamma && a.beta) ? a.beta[c] : 0.0f;
+    __stcg(ws_f4(a, a.plan.off_coef) + 2 * (size_t)c, make_float4(mf, g * r, bt, 0.f));
+  }
   a.mean[c] = mf;
   a.var[c] = vf;
   // running statistics: y <- y + rate*(x - y)  (OnlineAverageOp; reference tests/test_gpu.rs:561-593)
   if (a.run_mean) { const float o = a.run_mean[c]; a.run_mean[c] = o + a.avg_rate * (mf - o); }
   if (a.run_var) { const float o = a.run_var[c]; a.run_var[c] = o + a.avg_rate * (vf - o); }
-  const float g = a.gamma ? a.gamma[c] : 1.0f;
-  const float bt = (a.gamma && a.beta) ? a.beta[c] : 0.0f;
-  float4 *coef = ws_f4(a, a.plan.off_coef) + 2 * (size_t)c;
-  __stcg(coef, make_float4(mf, g * inv_std(vf), bt, 0.f));
 }
 
 // Backward: S1 = sum(dz), S2 = sum(dz*(x-mean)) of channel c over all tiles.  One thread.
@@ -107,13 +138,19 @@ __device__ __forceinline__ void finish_channel_bwd(const FusedArgs &a, uint32_t 
   const float g = a.gamma ? a.gamma[c] : 1.0f;
   const float bt = (a.gamma && a.beta) ? a.beta[c] : 0.0f;
   const double rs2 = (double)r * s2;                       // sum(dz * xhat)
-  if (a.dbeta) a.dbeta[c] = (float)s1;
-  if (a.dgamma) a.dgamma[c] = (float)rs2;
   const double A = (double)g * (double)r;
   const double invM = 1.0 / a.count_total;
-  float4 *coef = ws_f4(a, a.plan.off_coef) + 2 * (size_t)c;
-  __stcg(coef, make_float4(mf, g * r, bt, 0.f));
-  __stcg(coef + 1, make_float4((float)(-A * (double)r * rs2 * invM), (float)(-A * s1 * invM), 0.f, 0.f));
+  const float cB = (float)(-A * (double)r * rs2 * invM);
+  const float cC = __uint_as_float(__float_as_uint((float)(-A * s1 * invM)) | 1u);   // never all-zero bits
+  if (a.use_rec) {
+    st_release_gpu_u64(reinterpret_cast<unsigned long long *>(a.ws + a.plan.off_rec) + c, pack_rec(cB, cC));
+  } else {
+    float4 *coef = ws_f4(a, a.plan.off_coef) + 2 * (size_t)c;
+    __stcg(coef, make_float4(mf, g * r, bt, 0.f));
+    __stcg(coef + 1, make_float4(cB, cC, 0.f, 0.f));
+  }
+  if (a.dbeta) a.dbeta[c] = (float)s1;
+  if (a.dgamma) a.dgamma[c] = (float)rs2;
 }
 
 // Merge the partials of unit u.  Whole block; regime R (one channel, many partials).

@@ -1,0 +1,932 @@
+// Warp-specialised version of the fused batch-norm pipeline for the 128-bit paths.
+//
+// Same algorithm as bn_fused.cuh (reduce a tile, complete its unit, apply the tile a bounded
+// number of steps later), but no consumer thread ever waits on global memory:
+//
+//   producer warp    walks the block's schedule and streams tiles into a ring of shared-memory
+//                    slots with bulk asynchronous copies (cp.async.bulk + mbarrier), tagged
+//                    with L2 eviction hints: "keep" for the reduce visit, "drop" for the
+//                    apply visit.  The ring keeps HBM requests in flight while everything
+//                    else happens.
+//   consumer warps   (8) read slots with 128-bit shared loads, accumulate / normalise, write
+//                    results with 128-bit streaming stores, and hand partials to the delivery
+//                    warp through a shared-memory mailbox.  In regime R every warp works on its
+//                    own share of a tile and never synchronises with the other warps.
+//   delivery warp    moves partials from the mailbox to the workspace, counts them per unit and,
+//                    for the partial that completes a unit, merges all of the unit's partials
+//                    in double precision and publishes one tagged 64-bit record per channel.
+//   coefficient warp polls the records of the units of upcoming apply visits (a record is its
+//                    own ready flag) and stages the visit's coefficients in a second mailbox.
+//
+// Every wait is bounded: a wait that runs out sets a status bit, raises the block's abort flag
+// and all three roles drain and leave.
+#pragma once
+#include "bn_fused.cuh"
+
+namespace anode_b200 {
+
+constexpr uint32_t kConsumers = 256;
+constexpr uint32_t kRingThreads = kConsumers + 96;   // + producer, delivery and coefficient warps
+constexpr uint32_t kResQ = 4;                        // partial mailbox depth
+constexpr uint32_t kCoefQ = 4;                       // coefficient mailbox depth
+constexpr uint32_t kMaxSlots = 8;
+constexpr long long kWaitCycles = 3000000000ll;      // about 1.5 s at 2 GHz
+
+// Optional per-block cycle accounting (build with -DANODE_RING_PROFILE): 16 counters per block are
+// written behind the regular workspace contents.
+#ifdef ANODE_RING_PROFILE
+#define RING_PROF_DECL long long pf_t = clock64(); long long pf[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#define RING_PROF(i) { const long long pf_n = clock64(); pf[i] += pf_n - pf_t; pf_t = pf_n; }
+#define RING_PROF_OUT(base) { unsigned long long *pf_o = reinterpret_cast<unsigned long long *>(a.ws + a.ws_capacity - (1u << 20)) + 24 * (size_t)blockIdx.x + (base); for (int pf_i = 0; pf_i < 8; ++pf_i) pf_o[pf_i] = (unsigned long long)pf[pf_i]; }
+__device__ __forceinline__ unsigned long long gtimer() { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
+// timeline samples: [0..4095] publish time per channel; then 4 values per apply visit of block 0
+#define RING_TL(idx, val) { reinterpret_cast<unsigned long long *>(a.ws + a.ws_capacity - 512 * 1024)[idx] = (val); }
+#else
+#define RING_PROF_DECL
+#define RING_PROF(i) {}
+#define RING_PROF_OUT(base) {}
+#define RING_TL(idx, val) {}
+#endif
+
+struct RingCtl {
+  unsigned long long full[kMaxSlots], empty[kMaxSlots];
+  unsigned long long res_full[kResQ], res_empty[kResQ];
+  unsigned long long coef_full[kCoefQ], coef_empty[kCoefQ];
+  float mom[3 * (kConsumers / 32)];
+  volatile uint32_t abort;
+  uint32_t last_block;
+};
+
+// ---- mbarrier / bulk-copy primitives --------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(unsigned long long *bar, uint32_t count)
+{
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(unsigned long long *bar)
+{
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(unsigned long long *bar, uint32_t bytes)
+{
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_test(unsigned long long *bar, uint32_t parity)
+{
+  uint32_t ok;
+  asm volatile("{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+               : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool mbar_try(unsigned long long *bar, uint32_t parity)
+{
+  uint32_t ok;
+  // the last operand lets the hardware keep the thread suspended (up to that many nanoseconds)
+  // until the phase completes, instead of returning early to a polling loop
+  asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+               : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity), "r"(100000u) : "memory");
+  return ok != 0;
+}
+// Bounded wait.  Returns false (after raising the abort flag) when the barrier did not flip in time
+// or when another role already gave up.
+__device__ __forceinline__ bool mbar_wait(unsigned long long *bar, uint32_t parity, RingCtl *ctl, uint32_t *status, uint32_t bit)
+{
+  if (mbar_try(bar, parity)) return true;
+  const long long t0 = clock64();
+  uint32_t it = 0;
+  for (;;) {
+    if (mbar_try(bar, parity)) return true;
+    if (ctl->abort) return false;
+    if ((++it & 63u) == 0u && clock64() - t0 > kWaitCycles) {
+      atomicOr(status, bit);
+      ctl->abort = 1;
+      return false;
+    }
+  }
+}
+// One lane waits for the whole warp; every lane gets the same answer.
+__device__ __forceinline__ bool warp_wait(unsigned long long *bar, uint32_t parity, RingCtl *ctl, uint32_t *status, uint32_t bit)
+{
+  uint32_t ok = 1;
+  if ((threadIdx.x & 31) == 0) ok = mbar_wait(bar, parity, ctl, status, bit) ? 1u : 0u;
+  return __shfl_sync(0xffffffffu, ok, 0) != 0;
+}
+// global -> shared bulk copy, completion counted on `bar`; bytes and both addresses are multiples of 16
+__device__ __forceinline__ void bulk_g2s(void *dst, const void *src, uint32_t bytes, unsigned long long *bar, uint64_t policy)
+{
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;"
+               ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)), "l"(policy) : "memory");
+}
+__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kConsumers) : "memory"); }
+// Barrier over the consumer warps that also ANDs a predicate, so that the decision to go on or
+// to give up after a bounded wait is the same in every consumer thread.
+__device__ __forceinline__ bool consumer_all(bool ok)
+{
+  uint32_t r;
+  asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.u32 p, %1, 0;\n\tbar.red.and.pred q, 1, %2, p;\n\tselp.u32 %0, 1, 0, q;\n\t}"
+               : "=r"(r) : "r"((uint32_t)ok), "n"(kConsumers) : "memory");
+  return r != 0;
+}
+
+__device__ __forceinline__ Pack<4> lds4(const float *p)
+{
+  const float4 t = *reinterpret_cast<const float4 *>(p);
+  Pack<4> r; r.v[0] = t.x; r.v[1] = t.y; r.v[2] = t.z; r.v[3] = t.w; return r;
+}
+
+// Block-wide (consumer warps only) merge / sum; results valid in thread 0 / all threads.
+__device__ __forceinline__ Moments consumer_merge(Moments a, float *buf)
+{
+  constexpr int kWarps = kConsumers / 32;
+  a = warp_merge(a);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  consumer_sync();
+  if (lane == 0) { buf[warp] = a.n; buf[kWarps + warp] = a.mean; buf[2 * kWarps + warp] = a.m2; }
+  consumer_sync();
+  if (warp == 0) {
+    Moments b{0.f, 0.f, 0.f};
+    if (lane < kWarps) { b.n = buf[lane]; b.mean = buf[kWarps + lane]; b.m2 = buf[2 * kWarps + lane]; }
+#pragma unroll
+    for (int o = kWarps / 2; o > 0; o >>= 1) {
+      Moments c;
+      c.n = __shfl_down_sync(0xffffffffu, b.n, o);
+      c.mean = __shfl_down_sync(0xffffffffu, b.mean, o);
+      c.m2 = __shfl_down_sync(0xffffffffu, b.m2, o);
+      b = merge(b, c);
+    }
+    a = b;
+  }
+  return a;
+}
+__device__ __forceinline__ void consumer_sum2(float &a, float &b, float *buf)
+{
+  constexpr int kWarps = kConsumers / 32;
+  a = warp_sum(a); b = warp_sum(b);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  consumer_sync();
+  if (lane == 0) { buf[warp] = a; buf[kWarps + warp] = b; }
+  consumer_sync();
+  float ta = 0.f, tb = 0.f;
+#pragma unroll
+  for (int w = 0; w < kWarps; ++w) { ta += buf[w]; tb += buf[kWarps + w]; }
+  a = ta; b = tb;
+}
+
+// ---- the block's schedule --------------------------------------------------------------------
+// Operation k of a block: steps s = 0, 1, ...; at step s first REDUCE tile s (if any is left), then
+// APPLY tile s - look (if s >= look).  Every role walks this same sequence with its own cursor.
+struct Sched {
+  uint32_t my_tiles, look, b, G;
+  bool do_reduce, do_apply;
+  uint32_t s, phase;     // phase 0: reduce of step s pending; 1: apply of step s pending
+  __device__ __forceinline__ void init(const FusedArgs &a)
+  {
+    b = blockIdx.x; G = gridDim.x;
+    my_tiles = (b < a.plan.total_tiles) ? (a.plan.total_tiles - b + G - 1) / G : 0;
+    look = (a.mode == MODE_FUSED) ? a.plan.lookahead_steps : 0;
+    do_reduce = a.mode != MODE_APPLY; do_apply = a.mode != MODE_STATS;
+    s = 0; phase = 0;
+  }
+  // Advances to the next operation; returns false at the end.  kind: 0 reduce, 1 apply.
+  __device__ __forceinline__ bool next(uint32_t &kind, uint32_t &tile)
+  {
+    for (;;) {
+      if (s >= my_tiles + look) return false;
+      if (phase == 0) {
+        phase = 1;
+        if (do_reduce && s < my_tiles) { kind = 0; tile = b + s * G; return true; }
+      } else {
+        phase = 0;
+        const uint32_t ss = s++;
+        if (do_apply && ss >= look) { kind = 1; tile = b + (ss - look) * G; return true; }
+      }
+    }
+  }
+};
+
+struct RingGeom {
+  uint32_t slots, slot_floats, slot_stride, res_stride, off_res, off_coef, off_seg, off_slots, smem_bytes;
+};
+
+// dynamic shared memory accessors
+__device__ __forceinline__ float *slot_x(unsigned char *sm, const RingGeom &g, uint32_t slot) { return reinterpret_cast<float *>(sm + g.off_slots + (size_t)slot * g.slot_stride); }
+template <int DIR> __device__ __forceinline__ float *slot_dy(unsigned char *sm, const RingGeom &g, uint32_t slot) { return slot_x(sm, g, slot) + g.slot_floats; }
+template <int DIR> __device__ __forceinline__ float4 *slot_side(unsigned char *sm, const RingGeom &g, uint32_t slot)
+{
+  return reinterpret_cast<float4 *>(slot_x(sm, g, slot) + (DIR == 1 ? 2 : 1) * g.slot_floats);
+}
+__device__ __forceinline__ float4 *res_box(unsigned char *sm, const RingGeom &g, uint32_t q) { return reinterpret_cast<float4 *>(sm + g.off_res) + (size_t)q * g.res_stride; }
+__device__ __forceinline__ float4 *coef_box(unsigned char *sm, const RingGeom &g, uint32_t cb, uint32_t q) { return reinterpret_cast<float4 *>(sm + g.off_coef) + (size_t)q * cb * 2; }
+
+// ======================================================================================
+// consumer side
+// ======================================================================================
+// ---- regime R: each consumer warp handles vectors warp*32 + lane + i*256 of the tile ----------
+constexpr uint32_t kCWarps = kConsumers / 32;
+
+template <int DIR>
+__device__ __forceinline__ void warp_reduce_R(const FusedArgs &a, const RingGeom &g, unsigned char *sm, RingCtl *ctl,
+                                              const TileRange &tr, uint32_t slot, float4 *res)
+{
+  const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const float *xs = slot_x(sm, g, slot);
+  const uint32_t nvec = (tr.len / 4) * tr.rows;        // the slot holds the tile's rows back to back
+  if constexpr (DIR == 0) {
+    // shifted sums: K is this thread's first element (see bn_fused.cuh)
+    float K = 0.f;
+    if (tid < nvec) K = xs[4 * tid];
+    float s = 0.f, q = 0.f;
+    for (uint32_t j0 = tid; j0 < nvec; j0 += kConsumers * kUnroll) {
+      Pack<4> v[kUnroll];
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) {
+        const uint32_t j = j0 + u * kConsumers;
+        v[u] = (j < nvec) ? lds4(xs + 4 * (size_t)j) : pack_fill<4>(K);
+      }
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { const float d = v[u].v[i] - K; s += d; q = fmaf(d, d, q); }
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&ctl->empty[slot]);
+    Moments m{0.f, 0.f, 0.f};
+    if (tid < nvec) {
+      m.n = (float)(((nvec - tid + kConsumers - 1) / kConsumers) * 4);
+      const float inv = __fdividef(1.0f, m.n);
+      m.mean = fmaf(s, inv, K);
+      m.m2 = fmaxf(q - s * s * inv, 0.f);
+    }
+    m = warp_merge(m);
+    if (lane == 0) res[warp] = make_float4(m.n, m.mean, m.m2, 0.f);
+  } else {
+    const float *ds = slot_dy<1>(sm, g, slot);
+    const float4 cf = slot_side<1>(sm, g, slot)[0];
+    const float mean = cf.x, scale = cf.y, beta = cf.z;
+    const bool relu = a.relu != 0;
+    float s1 = 0.f, s2 = 0.f;
+    for (uint32_t j0 = tid; j0 < nvec; j0 += kConsumers * kUnroll) {
+      Pack<4> vx[kUnroll], vd[kUnroll];
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) {
+        const uint32_t j = j0 + u * kConsumers;
+        if (j < nvec) { vx[u] = lds4(xs + 4 * (size_t)j); vd[u] = lds4(ds + 4 * (size_t)j); }
+        else { vx[u] = pack_fill<4>(mean); vd[u] = pack_fill<4>(0.f); }
+      }
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float d = vx[u].v[i] - mean;
+          const float yb = fmaf(d, scale, beta);
+          const float dz = relu ? vd[u].v[i] * (yb > 0.0f ? 1.0f : 0.0f) : vd[u].v[i];
+          s1 += dz; s2 = fmaf(dz, d, s2);
+        }
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&ctl->empty[slot]);
+    s1 = warp_sum(s1); s2 = warp_sum(s2);
+    if (lane == 0) res[warp] = make_float4(s1, s2, 0.f, 0.f);
+  }
+}
+
+template <int DIR>
+__device__ __forceinline__ void warp_apply_R(const FusedArgs &a, const RingGeom &g, unsigned char *sm, RingCtl *ctl,
+                                             const TileRange &tr, uint32_t slot, const float4 *coef, uint32_t coef_q)
+{
+  const uint32_t tid = threadIdx.x, lane = tid & 31;
+  const float *xs = slot_x(sm, g, slot);
+  const float *ds = slot_dy<DIR>(sm, g, slot);
+  const bool relu = a.relu != 0, acc = a.accumulate != 0;
+  const uint64_t drop = policy_drop();
+  const uint64_t rs = (uint64_t)a.plan.C * a.plan.dim0;
+  float *out = a.out + tr.base;
+  const float4 c0 = coef[0], c1 = coef[1];
+  const float mean = c0.x, scale = c0.y, beta = c0.z, cB = c1.x, cC = c1.y;
+  const uint32_t per_row = tr.len / 4, nvec = per_row * tr.rows;
+  const uint32_t mul = a.plan.div_mul;       // rows > 1 only occurs with whole rows, where per_row matches it
+  for (uint32_t j0 = tid; j0 < nvec; j0 += kConsumers * kUnroll) {
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const uint32_t j = j0 + u * kConsumers;
+      if (j < nvec) {
+        const Pack<4> vx = lds4(xs + 4 * (size_t)j);
+        Pack<4> o;
+        size_t off = 4 * (size_t)j;
+        if (tr.rows != 1) { const uint32_t r = fast_div(j, mul); off = (size_t)r * rs + 4 * (size_t)(j - r * per_row); }
+        if constexpr (DIR == 0) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) { const float yb = fmaf(vx.v[i] - mean, scale, beta); o.v[i] = relu ? positive_clip(yb) : yb; }
+        } else {
+          const Pack<4> vd = lds4(ds + 4 * (size_t)j);
+          if (acc) o = Pack<4>::load(out + off);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float d = vx.v[i] - mean;
+            const float yb = fmaf(d, scale, beta);
+            const float dz = relu ? vd.v[i] * (yb > 0.0f ? 1.0f : 0.0f) : vd.v[i];
+            const float dx = fmaf(scale, dz, fmaf(cB, d, cC));
+            o.v[i] = acc ? o.v[i] + dx : dx;
+          }
+        }
+        o.store(out + off, drop);
+      }
+    }
+  }
+  __syncwarp();
+  if (lane == 0) { mbar_arrive(&ctl->empty[slot]); mbar_arrive(&ctl->coef_empty[coef_q]); }
+}
+
+// ---- regime S: the eight warps work on a tile together (block barriers) -------------------------
+template <int DIR>
+__device__ __forceinline__ void block_reduce_S(const FusedArgs &a, const RingGeom &g, unsigned char *sm, RingCtl *ctl,
+                                               const TileRange &tr, uint32_t slot, float4 *res)
+{
+  const uint32_t tid = threadIdx.x;
+  const float *xs = slot_x(sm, g, slot);
+  const bool relu = a.relu != 0;
+  {
+    // regime S: thread owns float4 positions tid, tid+256 of the segment in every sample of the tile
+    const uint32_t seg4 = tr.len / 4, seg = tr.len, d0 = a.plan.dim0;
+    float *sa = reinterpret_cast<float *>(sm + g.off_seg), *sb = sa + kSegMaxFloats;
+    if constexpr (DIR == 0) {
+      float K[kSegSlots][4], s[kSegSlots][4], q[kSegSlots][4];
+#pragma unroll
+      for (int k = 0; k < (int)kSegSlots; ++k) {
+        const uint32_t v = tid + k * kConsumers;
+        Pack<4> p = pack_fill<4>(0.f);
+        if (v < seg4) p = lds4(xs + 4 * (size_t)v);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { K[k][i] = p.v[i]; s[k][i] = 0.f; q[k][i] = 0.f; }
+      }
+      for (uint32_t r = 1; r < tr.rows; ++r) {
+#pragma unroll
+        for (int k = 0; k < (int)kSegSlots; ++k) {
+          const uint32_t v = tid + k * kConsumers;
+          if (v < seg4) {
+            const Pack<4> p = lds4(xs + (size_t)r * seg + 4 * (size_t)v);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) { const float d = p.v[i] - K[k][i]; s[k][i] += d; q[k][i] = fmaf(d, d, q[k][i]); }
+          }
+        }
+      }
+      __syncwarp(); if ((tid & 31) == 0) mbar_arrive(&ctl->empty[slot]);
+      const float nr = (float)tr.rows, inv = __fdividef(1.0f, nr);
+      consumer_sync();   // sa / sb free (previous tile's channel pass is over)
+#pragma unroll
+      for (int k = 0; k < (int)kSegSlots; ++k) {
+        const uint32_t v = tid + k * kConsumers;
+        if (v < seg4) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            sa[4 * v + i] = fmaf(s[k][i], inv, K[k][i]);
+            sb[4 * v + i] = fmaxf(q[k][i] - s[k][i] * s[k][i] * inv, 0.f);
+          }
+        }
+      }
+      consumer_sync();
+      for (uint32_t ci = tid; ci < tr.cw; ci += kConsumers) {
+        const float *pm = sa + ci * d0, *pq = sb + ci * d0;
+        float smn = 0.f;
+        for (uint32_t i = 0; i < d0; ++i) smn += pm[i];
+        const float mean = smn / (float)d0;
+        float m2 = 0.f, dev = 0.f;
+        for (uint32_t i = 0; i < d0; ++i) { const float d = pm[i] - mean; m2 += pq[i]; dev = fmaf(d, d, dev); }
+        res[ci] = make_float4(nr * (float)d0, mean, fmaf(nr, dev, m2), 0.f);
+      }
+      consumer_sync();
+    } else {
+      const float *ds = slot_dy<1>(sm, g, slot);
+      const float4 *side = slot_side<1>(sm, g, slot);
+      float cm[kSegSlots][4], cs[kSegSlots][4], cbt[kSegSlots][4], s1[kSegSlots][4], s2[kSegSlots][4];
+#pragma unroll
+      for (int k = 0; k < (int)kSegSlots; ++k) {
+        const uint32_t v = tid + k * kConsumers;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const uint32_t ci = (v < seg4) ? (4 * v + i) / d0 : 0;
+          const float4 cf = side[ci];
+          cm[k][i] = cf.x; cs[k][i] = cf.y; cbt[k][i] = cf.z; s1[k][i] = 0.f; s2[k][i] = 0.f;
+        }
+      }
+      for (uint32_t r = 0; r < tr.rows; ++r) {
+#pragma unroll
+        for (int k = 0; k < (int)kSegSlots; ++k) {
+          const uint32_t v = tid + k * kConsumers;
+          if (v < seg4) {
+            const Pack<4> px = lds4(xs + (size_t)r * seg + 4 * (size_t)v), pd = lds4(ds + (size_t)r * seg + 4 * (size_t)v);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const float d = px.v[i] - cm[k][i];
+              const float yb = fmaf(d, cs[k][i], cbt[k][i]);
+              const float dz = relu ? pd.v[i] * (yb > 0.0f ? 1.0f : 0.0f) : pd.v[i];
+              s1[k][i] += dz; s2[k][i] = fmaf(dz, d, s2[k][i]);
+            }
+          }
+        }
+      }
+      __syncwarp(); if ((tid & 31) == 0) mbar_arrive(&ctl->empty[slot]);
+      consumer_sync();
+#pragma unroll
+      for (int k = 0; k < (int)kSegSlots; ++k) {
+        const uint32_t v = tid + k * kConsumers;
+        if (v < seg4) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) { sa[4 * v + i] = s1[k][i]; sb[4 * v + i] = s2[k][i]; }
+        }
+      }
+      consumer_sync();
+      for (uint32_t ci = tid; ci < tr.cw; ci += kConsumers) {
+        const float *p1 = sa + ci * d0, *p2 = sb + ci * d0;
+        float t1 = 0.f, t2 = 0.f;
+        for (uint32_t i = 0; i < d0; ++i) { t1 += p1[i]; t2 += p2[i]; }
+        res[ci] = make_float4(t1, t2, 0.f, 0.f);
+      }
+      consumer_sync();
+    }
+  }
+}
+
+template <int DIR>
+__device__ __forceinline__ void block_apply_S(const FusedArgs &a, const RingGeom &g, unsigned char *sm, RingCtl *ctl,
+                                              const TileRange &tr, uint32_t slot, const float4 *coef, uint32_t coef_q)
+{
+  const uint32_t tid = threadIdx.x;
+  const float *xs = slot_x(sm, g, slot);
+  const float *ds = slot_dy<DIR>(sm, g, slot);
+  const bool relu = a.relu != 0, acc = a.accumulate != 0;
+  const uint64_t drop = policy_drop();
+  const uint64_t rs = (uint64_t)a.plan.C * a.plan.dim0;
+  float *out = a.out + tr.base;
+  {
+    const uint32_t seg4 = tr.len / 4, seg = tr.len, d0 = a.plan.dim0;
+    float cm[kSegSlots][4], cs[kSegSlots][4], cbt[kSegSlots][4], cB[kSegSlots][4], cC[kSegSlots][4];
+#pragma unroll
+    for (int k = 0; k < (int)kSegSlots; ++k) {
+      const uint32_t v = tid + k * kConsumers;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const uint32_t ci = (v < seg4) ? (4 * v + i) / d0 : 0;
+        const float4 c0 = coef[2 * ci];
+        cm[k][i] = c0.x; cs[k][i] = c0.y; cbt[k][i] = c0.z;
+        if constexpr (DIR == 1) { const float4 c1 = coef[2 * ci + 1]; cB[k][i] = c1.x; cC[k][i] = c1.y; }
+      }
+    }
+    __syncwarp(); if ((tid & 31) == 0) mbar_arrive(&ctl->coef_empty[coef_q]);
+    for (uint32_t r = 0; r < tr.rows; ++r) {
+#pragma unroll
+      for (int k = 0; k < (int)kSegSlots; ++k) {
+        const uint32_t v = tid + k * kConsumers;
+        if (v < seg4) {
+          const size_t so = (size_t)r * seg + 4 * (size_t)v, off = (size_t)r * rs + 4 * (size_t)v;
+          const Pack<4> px = lds4(xs + so);
+          Pack<4> o;
+          if constexpr (DIR == 0) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) { const float yb = fmaf(px.v[i] - cm[k][i], cs[k][i], cbt[k][i]); o.v[i] = relu ? positive_clip(yb) : yb; }
+          } else {
+            const Pack<4> pd = lds4(ds + so);
+            if (acc) o = Pack<4>::load(out + off);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const float d = px.v[i] - cm[k][i];
+              const float yb = fmaf(d, cs[k][i], cbt[k][i]);
+              const float dz = relu ? pd.v[i] * (yb > 0.0f ? 1.0f : 0.0f) : pd.v[i];
+              const float dx = fmaf(cs[k][i], dz, fmaf(cB[k][i], d, cC[k][i]));
+              o.v[i] = acc ? o.v[i] + dx : dx;
+            }
+          }
+          o.store(out + off, drop);
+        }
+      }
+    }
+    __syncwarp(); if ((tid & 31) == 0) mbar_arrive(&ctl->empty[slot]);
+  }
+}
+
+// ======================================================================================
+// delivery warp: unit completion
+// ======================================================================================
+// (count, mean, M2) in double precision and Chan's pairwise update; used to merge a unit's
+// partials in ONE pass over them, so that every partial is loaded exactly once and all loads
+// of a batch are in flight together (the merge sits on the critical path of the pipeline).
+struct Moments64 { double n, mean, m2; };
+__device__ __forceinline__ Moments64 merge64(Moments64 a, Moments64 b)
+{
+  const double n = a.n + b.n;
+  if (n <= 0.0) return Moments64{0.0, 0.0, 0.0};
+  const double f = b.n / n, d = b.mean - a.mean;
+  return Moments64{n, a.mean + d * f, a.m2 + b.m2 + d * d * a.n * f};
+}
+__device__ __forceinline__ Moments64 warp_merge64(Moments64 a)
+{
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    Moments64 b;
+    b.n = __shfl_down_sync(0xffffffffu, a.n, o);
+    b.mean = __shfl_down_sync(0xffffffffu, a.mean, o);
+    b.m2 = __shfl_down_sync(0xffffffffu, a.m2, o);
+    a = merge64(a, b);
+  }
+  return a;
+}
+constexpr int kFinBatch = 8;     // partial loads a lane keeps in flight (regime S)
+constexpr int kFinRegs = 16;     // partials a lane holds in registers (regime R: 512 tiles per unit)
+
+// Regime R: one channel, up to thousands of partials.  The merge sits on the critical path of the
+// pipeline, so all of a lane's loads are issued together (one round trip) and both passes of the
+// two-pass merge (weighted mean, then M2 about it) run from registers.  Units with more than
+// 32*kFinRegs tiles take further rounds and fold each round in with Chan's update.
+template <int DIR>
+__device__ __forceinline__ void warp_finish_unit_R(const FusedArgs &a, uint32_t u)
+{
+  const Plan &P = a.plan;
+  const uint32_t lane = threadIdx.x & 31, T = P.tiles_per_unit;
+  const float4 *part = ws_f4(a, P.off_part) + (size_t)u * T;
+  Moments64 tot{0.0, 0.0, 0.0};
+  double s1 = 0.0, s2 = 0.0;
+  for (uint32_t k0 = 0; k0 < T; k0 += 32u * kFinRegs) {
+    float rx[kFinRegs], ry[kFinRegs], rz[kFinRegs];
+#pragma unroll
+    for (int i = 0; i < kFinRegs; ++i) {
+      const uint32_t k = k0 + lane + 32u * i;
+      const float4 p = (k < T) ? __ldcg(part + k) : make_float4(0.f, 0.f, 0.f, 0.f);
+      rx[i] = p.x; ry[i] = p.y; rz[i] = p.z;
+    }
+    if constexpr (DIR == 0) {
+      double sn = 0.0, sm = 0.0;
+#pragma unroll
+      for (int i = 0; i < kFinRegs; ++i) { sn += (double)rx[i]; sm = fma((double)rx[i], (double)ry[i], sm); }
+      sn = warp_sum_all(sn); sm = warp_sum_all(sm);
+      const double mean = sn > 0.0 ? sm / sn : 0.0;
+      double sq = 0.0;
+#pragma unroll
+      for (int i = 0; i < kFinRegs; ++i) { const double d = (double)ry[i] - mean; sq += (double)rz[i] + (double)rx[i] * d * d; }
+      sq = warp_sum_all(sq);
+      tot = merge64(tot, Moments64{sn, mean, sq});
+    } else {
+#pragma unroll
+      for (int i = 0; i < kFinRegs; ++i) { s1 += (double)rx[i]; s2 += (double)ry[i]; }
+    }
+  }
+  if constexpr (DIR == 0) {
+    if (lane == 0) finish_channel_fwd(a, u, tot.n, tot.mean, tot.m2);
+  } else {
+    s1 = warp_sum_all(s1); s2 = warp_sum_all(s2);
+    if (lane == 0) finish_channel_bwd(a, u, s1, s2);
+  }
+}
+
+// Regime S: a block of channels with few partials each; one lane per channel, 32 channels at a time.
+template <int DIR>
+__device__ __forceinline__ void warp_finish_unit_S(const FusedArgs &a, uint32_t u)
+{
+  const Plan &P = a.plan;
+  const uint32_t lane = threadIdx.x & 31, T = P.tiles_per_unit;
+  const uint32_t c0 = u * P.cb;
+  const uint32_t cw = (P.C - c0 < P.cb) ? (P.C - c0) : P.cb;
+  const float4 *part = ws_f4(a, P.off_part) + (size_t)u * T * P.cb;
+  for (uint32_t cbase = 0; cbase < cw; cbase += 32) {
+    const uint32_t ci = cbase + lane;
+    const bool live = ci < cw;
+    Moments64 acc{0.0, 0.0, 0.0};
+    double s1 = 0.0, s2 = 0.0;
+    for (uint32_t k0 = 0; k0 < T; k0 += kFinBatch) {
+      float4 reg[kFinBatch];
+#pragma unroll
+      for (int i = 0; i < kFinBatch; ++i) {
+        const uint32_t k = k0 + i;
+        reg[i] = (live && k < T) ? __ldcg(part + (size_t)k * P.cb + ci) : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+#pragma unroll
+      for (int i = 0; i < kFinBatch; ++i) {
+        if constexpr (DIR == 0) acc = merge64(acc, Moments64{(double)reg[i].x, (double)reg[i].y, (double)reg[i].z});
+        else { s1 += (double)reg[i].x; s2 += (double)reg[i].y; }
+      }
+    }
+    if (live) {
+      if constexpr (DIR == 0) finish_channel_fwd(a, c0 + ci, acc.n, acc.mean, acc.m2);
+      else finish_channel_bwd(a, c0 + ci, s1, s2);
+    }
+  }
+}
+
+// ======================================================================================
+// the kernel
+// ======================================================================================
+template <int DIR, int REGIME>
+__global__ void __launch_bounds__(kRingThreads, 2) bn_ring_kernel(const FusedArgs a, const RingGeom g)
+{
+  extern __shared__ __align__(128) unsigned char sm[];
+  RingCtl *ctl = reinterpret_cast<RingCtl *>(sm);
+  const Plan &P = a.plan;
+  const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  uint32_t *status = ws_u32(a, 0);
+  uint32_t *exit_ctr = ws_u32(a, 4);
+  uint32_t *done = ws_u32(a, P.off_done);
+
+  if (tid == 0) {
+    for (uint32_t i = 0; i < g.slots; ++i) { mbar_init(&ctl->full[i], 1); mbar_init(&ctl->empty[i], kCWarps); }
+    for (uint32_t i = 0; i < kResQ; ++i) { mbar_init(&ctl->res_full[i], kCWarps); mbar_init(&ctl->res_empty[i], 1); }
+    for (uint32_t i = 0; i < kCoefQ; ++i) { mbar_init(&ctl->coef_full[i], 1); mbar_init(&ctl->coef_empty[i], kCWarps); }
+    ctl->abort = 0; ctl->last_block = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  __syncthreads();
+
+  Sched sc; sc.init(a);
+  uint32_t kind, tile;
+
+  if (warp < kConsumers / 32) {
+    // ------------------------------------------------------------------ consumers
+    uint32_t k = 0, nres = 0, ncoef = 0;      // ring position, reduce count, apply count
+    RING_PROF_DECL
+    while (sc.next(kind, tile)) {
+      const uint32_t slot = k % g.slots, par = (k / g.slots) & 1u; ++k;
+      const TileRange tr = tile_range(P, tile);
+      if (kind == 0) {
+        const uint32_t q = nres % kResQ, qpar = (nres / kResQ) & 1u; ++nres;
+        // the partial mailbox entry must have been emptied by the delivery warp (first pass: free)
+        bool ok = warp_wait(&ctl->res_empty[q], qpar ^ 1u, ctl, status, ANODE_ST_WAIT_STATS);
+        RING_PROF(0)
+        ok = ok && warp_wait(&ctl->full[slot], par, ctl, status, ANODE_ST_WAIT_STATS);
+        RING_PROF(1)
+        if constexpr (REGIME == 0) {
+          if (!ok) break;                               // warps are independent: no barrier to honour
+          warp_reduce_R<DIR>(a, g, sm, ctl, tr, slot, res_box(sm, g, q));
+          if (lane == 0) mbar_arrive(&ctl->res_full[q]);
+        } else {
+          if (!consumer_all(ok)) break;                 // same decision in all eight warps
+          block_reduce_S<DIR>(a, g, sm, ctl, tr, slot, res_box(sm, g, q));
+          if (lane == 0) mbar_arrive(&ctl->res_full[q]);
+        }
+        RING_PROF(3)
+      } else {
+        const uint32_t q = ncoef % kCoefQ, qpar = (ncoef / kCoefQ) & 1u; ++ncoef;
+#ifdef ANODE_RING_PROFILE
+        const unsigned long long tl_need = gtimer();
+#endif
+        bool ok = warp_wait(&ctl->coef_full[q], qpar, ctl, status, ANODE_ST_WAIT_STATS);
+#ifdef ANODE_RING_PROFILE
+        if (blockIdx.x == 0 && tid == 0 && ncoef <= 256) { RING_TL(4096 + 4 * (ncoef - 1), tl_need) RING_TL(4096 + 4 * (ncoef - 1) + 1, gtimer()) RING_TL(4096 + 4 * (ncoef - 1) + 2, (unsigned long long)tr.unit) }
+#endif
+        RING_PROF(4)
+        ok = ok && warp_wait(&ctl->full[slot], par, ctl, status, ANODE_ST_WAIT_STATS);
+        RING_PROF(5)
+        if constexpr (REGIME == 0) {
+          if (!ok) break;
+          warp_apply_R<DIR>(a, g, sm, ctl, tr, slot, coef_box(sm, g, P.cb, q), q);
+        } else {
+          if (!consumer_all(ok)) break;
+          block_apply_S<DIR>(a, g, sm, ctl, tr, slot, coef_box(sm, g, P.cb, q), q);
+        }
+        RING_PROF(7)
+      }
+    }
+    if (tid == 0) RING_PROF_OUT(0)
+  } else if (warp == kConsumers / 32) {
+    // ------------------------------------------------------------------ producer
+    const uint64_t keep = policy_keep(), drop = policy_drop();
+    const uint64_t rs = (uint64_t)P.C * P.dim0;
+    uint32_t k = 0;
+    bool ok = true;
+    RING_PROF_DECL
+    while (ok && sc.next(kind, tile)) {
+      const uint32_t slot = k % g.slots, par = (k / g.slots) & 1u; ++k;
+      const TileRange tr = tile_range(P, tile);
+      uint32_t okw = 1;
+      if (lane == 0) okw = mbar_wait(&ctl->empty[slot], par ^ 1u, ctl, status, ANODE_ST_WAIT_STATS) ? 1u : 0u;
+      ok = __shfl_sync(0xffffffffu, okw, 0) != 0;     // one lane decides for the warp
+      RING_PROF(0)
+      if (!ok) { --k; break; }
+      float *xs = slot_x(sm, g, slot);
+      if (DIR == 1 && kind == 0) {
+        // coefficients of the reduce visit's ReLU mask, per channel of the unit
+        float4 *side = slot_side<1>(sm, g, slot);
+        for (uint32_t ci = lane; ci < tr.cw; ci += 32) {
+          const uint32_t c = tr.c0 + ci;
+          const float gm = a.gamma ? a.gamma[c] : 1.0f;
+          side[ci] = make_float4(a.mean_in[c], gm * inv_std(a.var_in[c]), (a.gamma && a.beta) ? a.beta[c] : 0.0f, 0.f);
+        }
+      }
+      __syncwarp();
+      const uint32_t row_bytes = tr.len * 4u;
+      if (lane == 0) mbar_arrive_expect_tx(&ctl->full[slot], row_bytes * tr.rows * (DIR == 1 ? 2u : 1u));
+      __syncwarp();
+      const uint64_t pol = (kind == 0 && a.mode == MODE_FUSED) ? keep : drop;
+      for (uint32_t r = lane; r < tr.rows; r += 32) {
+        const size_t goff = (size_t)tr.base + (size_t)r * rs;
+        bulk_g2s(xs + (size_t)r * tr.len, a.x + goff, row_bytes, &ctl->full[slot], pol);
+        if (DIR == 1) bulk_g2s(xs + g.slot_floats + (size_t)r * tr.len, a.dy + goff, row_bytes, &ctl->full[slot], pol);
+      }
+      RING_PROF(1)
+    }
+    if (lane == 0) RING_PROF_OUT(8)
+    // after an abort: wait (bounded) for copies that were issued but will not be consumed
+    if (!ok && lane == 0) {
+      const uint32_t first = k > g.slots ? k - g.slots : 0;
+      for (uint32_t kk = first; kk < k; ++kk) {
+        const long long t0 = clock64();
+        while (!mbar_test(&ctl->full[kk % g.slots], (kk / g.slots) & 1u) && clock64() - t0 < kWaitCycles / 8) {}
+      }
+    }
+  } else if (warp == kConsumers / 32 + 1) {
+    // ------------------------------------------------------------------ delivery warp
+    // Reduce visit j of this block is tile b + j*G.  Each turn serves every partial that waits,
+    // one lane per partial, so the fences and atomics of several tiles overlap.
+    const uint32_t n_red = sc.do_reduce ? sc.my_tiles : 0;
+    uint32_t nres = 0;
+    RING_PROF_DECL
+    while (nres < n_red) {
+      // sleep on the next entry's barrier (no polling loop competing with the consumers for issue
+      // slots), then take along whatever else has arrived in the meantime
+      if (!warp_wait(&ctl->res_full[nres % kResQ], (nres / kResQ) & 1u, ctl, status, ANODE_ST_WAIT_STATS)) break;
+#ifdef ANODE_RING_PROFILE
+      const unsigned long long tl_pick = gtimer();
+#endif
+      const uint32_t jd = nres + lane;
+      const bool d_ok = lane < kResQ && jd < n_red && mbar_test(&ctl->res_full[jd % kResQ], (jd / kResQ) & 1u);
+      const uint32_t d_mask = __ballot_sync(0xffffffffu, d_ok);
+      const uint32_t nd = __ffs(~d_mask) - 1;                         // in order: leading run of ones
+      RING_PROF(0)
+      if (nd) {
+        if constexpr (REGIME == 0) {
+          // entry e is served by lanes 8e .. 8e+7: one warp partial each, merged in a fixed order
+          const uint32_t e = lane >> 3, w = lane & 7u;
+          float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+          if (e < nd) v = res_box(sm, g, (nres + e) % kResQ)[w];
+          if constexpr (DIR == 0) {
+            Moments m{v.x, v.y, v.z};
+#pragma unroll
+            for (int o = 4; o > 0; o >>= 1) {
+              Moments c;
+              c.n = __shfl_down_sync(0xffffffffu, m.n, o, 8);
+              c.mean = __shfl_down_sync(0xffffffffu, m.mean, o, 8);
+              c.m2 = __shfl_down_sync(0xffffffffu, m.m2, o, 8);
+              m = merge(m, c);
+            }
+            v = make_float4(m.n, m.mean, m.m2, 0.f);
+          } else {
+#pragma unroll
+            for (int o = 4; o > 0; o >>= 1) {
+              v.x += __shfl_down_sync(0xffffffffu, v.x, o, 8);
+              v.y += __shfl_down_sync(0xffffffffu, v.y, o, 8);
+            }
+          }
+          if (e < nd && w == 0) __stcg(ws_f4(a, P.off_part) + (size_t)(sc.b + (nres + e) * sc.G), v);
+        } else {
+          for (uint32_t e = 0; e < nd; ++e) {
+            const uint32_t j = nres + e, t = sc.b + j * sc.G;
+            const uint32_t c0 = (t / P.tiles_per_unit) * P.cb;
+            const uint32_t cw = (P.C - c0 < P.cb) ? (P.C - c0) : P.cb;
+            const float4 *res = res_box(sm, g, j % kResQ);
+            float4 *part = ws_f4(a, P.off_part) + (size_t)t * P.cb;
+            for (uint32_t ci = lane; ci < cw; ci += 32) __stcg(part + ci, res[ci]);
+          }
+        }
+        __syncwarp();
+        uint32_t last = 0, unit = 0;
+        if (lane < nd) {
+          const uint32_t j = nres + lane;
+          unit = (sc.b + j * sc.G) / P.tiles_per_unit;
+          mbar_arrive(&ctl->res_empty[j % kResQ]);
+          // release: the partial stored above is visible before the count; acquire: whoever sees the
+          // full count also sees every partial counted before
+          uint32_t old;
+          asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], 1;" : "=r"(old) : "l"(done + unit) : "memory");
+          last = (old + 1 == P.tiles_per_unit) ? 1u : 0u;
+        }
+        uint32_t lmask = __ballot_sync(0xffffffffu, last != 0);
+        RING_PROF(1)
+#ifdef ANODE_RING_PROFILE
+        const unsigned long long tl_atom = gtimer();
+#endif
+        while (lmask) {
+          const uint32_t src = __ffs(lmask) - 1; lmask &= lmask - 1;
+          const uint32_t u = __shfl_sync(0xffffffffu, unit, src);
+          if constexpr (REGIME == 0) warp_finish_unit_R<DIR>(a, u); else warp_finish_unit_S<DIR>(a, u);
+          if (lane == 0) done[u] = 0;
+#ifdef ANODE_RING_PROFILE
+          if (lane == 0) { RING_TL(u, gtimer()) RING_TL(8192 + 2 * u, tl_pick) RING_TL(8192 + 2 * u + 1, tl_atom) }
+#endif
+          RING_PROF(2)
+        }
+        nres += nd;
+#ifdef ANODE_RING_PROFILE
+        pf[4] += nd; pf[5] += 1;
+#endif
+      }
+    }
+    if (lane == 0) RING_PROF_OUT(16)
+  } else {
+    // ------------------------------------------------------------------ coefficient warp
+    // Apply visit j of this block is tile b + j*G.  Lane e looks after visit ncoef + e: it polls the
+    // tagged records of the visit's channels (zero = not ready yet) and, once all are there, the
+    // warp assembles (mean, scale, beta | B, C0) per channel into the visit's mailbox entry.
+    const uint32_t n_app = sc.do_apply ? sc.my_tiles : 0;
+    const unsigned long long *rec = reinterpret_cast<const unsigned long long *>(a.ws + P.off_rec);
+    uint32_t ncoef = 0;
+    long long t_idle = clock64();
+    while (ncoef < n_app) {
+      if (!warp_wait(&ctl->coef_empty[ncoef % kCoefQ], ((ncoef / kCoefQ) & 1u) ^ 1u, ctl, status, ANODE_ST_WAIT_STATS)) break;
+      const uint32_t ja = ncoef + lane;
+      bool a_ok = lane < kCoefQ && ja < n_app && mbar_test(&ctl->coef_empty[ja % kCoefQ], ((ja / kCoefQ) & 1u) ^ 1u);
+      uint32_t c0 = 0, cw = 0;
+      unsigned long long r0 = 0;
+      float in_mean = 0.f, in_scale = 1.f, in_beta = 0.f;
+      if (a_ok) {
+        const uint32_t t = sc.b + ja * sc.G;
+        c0 = (t / P.tiles_per_unit) * P.cb;
+        cw = (P.C - c0 < P.cb) ? (P.C - c0) : P.cb;
+        if (a.mode == MODE_FUSED) {
+          if constexpr (REGIME == 0) {
+            // the inputs do not depend on the record: fetch them in the same round trip
+            const float gm = a.gamma ? a.gamma[c0] : 1.0f;
+            in_beta = (a.gamma && a.beta) ? a.beta[c0] : 0.0f;
+            if constexpr (DIR == 1) { in_mean = a.mean_in[c0]; in_scale = gm * inv_std(a.var_in[c0]); } else { in_scale = gm; }
+            r0 = ld_acquire_gpu_u64(rec + c0);
+            a_ok = r0 != 0ull;
+          } else {
+            for (uint32_t ci = 0; ci < cw && a_ok; ++ci) a_ok = ld_acquire_gpu_u64(rec + c0 + ci) != 0ull;
+          }
+        }
+      }
+      const uint32_t a_mask = __ballot_sync(0xffffffffu, a_ok);
+      const uint32_t na = __ffs(~a_mask) - 1;
+      if (__shfl_sync(0xffffffffu, (uint32_t)ctl->abort, 0)) break;
+      if (na) {
+        if (REGIME == 0 && a.mode == MODE_FUSED) {
+          // lane e completes entry e on its own from what it already holds
+          if (lane < na) {
+            float4 *box = coef_box(sm, g, P.cb, (ncoef + lane) % kCoefQ);
+            const float lo = __uint_as_float((uint32_t)(r0 & 0xffffffffull)), hi = __uint_as_float((uint32_t)(r0 >> 32));
+            if constexpr (DIR == 0) {
+              box[0] = make_float4(lo, in_scale * hi, in_beta, 0.f);            // (mean, gamma*rstd, beta)
+              box[1] = make_float4(0.f, 0.f, 0.f, 0.f);
+            } else {
+              box[0] = make_float4(in_mean, in_scale, in_beta, 0.f);
+              box[1] = make_float4(lo, hi, 0.f, 0.f);                           // (B, C0)
+            }
+          }
+        } else {
+          for (uint32_t e = 0; e < na; ++e) {
+            const uint32_t ec0 = __shfl_sync(0xffffffffu, c0, e), ecw = __shfl_sync(0xffffffffu, cw, e);
+            float4 *box = coef_box(sm, g, P.cb, (ncoef + e) % kCoefQ);
+            for (uint32_t ci = lane; ci < ecw; ci += 32) {
+              const uint32_t c = ec0 + ci;
+              if (a.mode != MODE_FUSED) {
+                // coefficients were prepared by a separate merge kernel
+                const float4 *coef = ws_f4(a, P.off_coef) + 2 * (size_t)c;
+                box[2 * ci] = __ldcg(coef); box[2 * ci + 1] = __ldcg(coef + 1);
+              } else {
+                const unsigned long long rv = ld_acquire_gpu_u64(rec + c);
+                const float lo = __uint_as_float((uint32_t)(rv & 0xffffffffull)), hi = __uint_as_float((uint32_t)(rv >> 32));
+                const float gm = a.gamma ? a.gamma[c] : 1.0f;
+                const float bt = (a.gamma && a.beta) ? a.beta[c] : 0.0f;
+                if constexpr (DIR == 0) {
+                  box[2 * ci] = make_float4(lo, gm * hi, bt, 0.f);
+                  box[2 * ci + 1] = make_float4(0.f, 0.f, 0.f, 0.f);
+                } else {
+                  box[2 * ci] = make_float4(a.mean_in[c], gm * inv_std(a.var_in[c]), bt, 0.f);
+                  box[2 * ci + 1] = make_float4(lo, hi, 0.f, 0.f);
+                }
+              }
+            }
+          }
+        }
+        __syncwarp();
+        if (lane < na) mbar_arrive(&ctl->coef_full[(ncoef + lane) % kCoefQ]);
+        ncoef += na;
+        t_idle = clock64();
+      } else {
+        __nanosleep(200);      // the unit is not complete yet: look again a little later
+        uint32_t give_up = 0;
+        if (lane == 0 && clock64() - t_idle > kWaitCycles) { atomicOr(status, ANODE_ST_WAIT_STATS); ctl->abort = 1; give_up = 1; }
+        if (__shfl_sync(0xffffffffu, give_up, 0)) break;
+      }
+    }
+  }
+
+  // ---- leave: the last block out lowers the ready flags so that the workspace is clean again
+  __syncthreads();
+  if (ctl->abort) {
+    if (tid == 0) atomicOr(status, ANODE_ST_ABORTED);
+    return;
+  }
+  if (a.mode == MODE_FUSED) {
+    if (tid == 0) {
+      __threadfence();
+      ctl->last_block = (atomicAdd(exit_ctr, 1u) + 1 == gridDim.x) ? 1u : 0u;
+    }
+    __syncthreads();
+    if (ctl->last_block) {
+      unsigned long long *rec = reinterpret_cast<unsigned long long *>(a.ws + P.off_rec);
+      for (uint32_t c = tid; c < P.C; c += kRingThreads) rec[c] = 0ull;
+      if (tid == 0) *exit_ctr = 0;
+    }
+  }
+}
+
+}  // namespace anode_b200
