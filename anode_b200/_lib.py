@@ -52,6 +52,15 @@ SIGNATURES = {
     "anode_gpu_batch_norm_relu_fused_bwd_3d1_packed_f32":
         (c_int, _D + [c_int, c_int] + [vp] * 9 + [vp, size_t] + _T),
     "anode_gpu_online_average_f32": (c_int, [u32, f32, vp, vp] + _T),
+    "anode_gpu_sync_unique_id_bytes": (size_t, []),
+    "anode_gpu_sync_get_unique_id": (c_int, [vp]),
+    "anode_gpu_sync_comm_create": (c_int, [vp, c_int, c_int, ctypes.POINTER(vp)]),
+    "anode_gpu_sync_comm_destroy": (c_int, [vp]),
+    "anode_gpu_sync_batch_norm_workspace_bytes": (size_t, _D + [c_int]),
+    "anode_gpu_sync_batch_norm_relu_fwd_3d1_packed_f32":
+        (c_int, _D + [f32, f32, c_int] + [vp] * 8 + [vp, vp, size_t] + _T),
+    "anode_gpu_sync_batch_norm_relu_bwd_3d1_packed_f32":
+        (c_int, _D + [ctypes.c_uint64, c_int, c_int] + [vp] * 9 + [vp, vp, size_t] + _T),
     "anode_gpu_batch_norm_fused_plan": (c_int, _D + [c_int, u32, u32, u32, ctypes.POINTER(u32), u32]),
     "anode_gpu_batch_norm_fused_plan_tile":
         (c_int, _D + [c_int, u32, u32, u32, ctypes.POINTER(ctypes.c_uint64)]),

@@ -39,5 +39,7 @@ int prepare_bwd(FusedArgs &a, uint32_t dim0, uint32_t dim1, uint32_t dim2, int r
                 const float *dy, const float *x, const float *mean, const float *var, const float *gamma,
                 const float *beta, float *dx, float *dgamma, float *dbeta, void *ws, size_t ws_bytes);
 int launch_pipeline(FusedArgs &a, int dir, cudaStream_t stream);
+// picks the warp-specialised kernel where it applies, the plain one otherwise
+int launch_best(FusedArgs &a, int dir, bool aligned, cudaStream_t stream);
 
 }  // namespace anode_b200

@@ -1,0 +1,197 @@
+// Synchronized batch-norm across the GPUs of one node: every rank holds a shard of the batch
+// (or a spatial slab) with all C channels, runs the local reduce pass, exchanges 16 bytes per
+// channel, and applies with the global statistics.
+//
+// The reference has no such path: its batch-norm is per process and its only collective is a
+// host-staged MPI allreduce of gradients (src/proc_mpi.rs:138-148, src/ops_gpu.rs:538-545).
+// Parity definition: G-way result == the single-device kernels run on the concatenated batch.
+//
+// Exchange through NCCL: all-gather of the local (count, mean, M2) resp. (sum dz, sum dz*(x-mean))
+// records, then every rank merges the G records of a channel in rank order in double precision,
+// so all ranks obtain bit-identical statistics.  NCCL is resolved at run time (dlopen of the
+// copy already loaded in the process, e.g. the one PyTorch ships), never linked.
+#include <dlfcn.h>
+#include <nccl.h>
+
+#include <cstring>
+
+#include "bn_host.h"
+#include "bn_sync.h"
+
+namespace anode_b200 {
+
+// ---- NCCL entry points, looked up once ----------------------------------------------------
+struct NcclApi {
+  ncclResult_t (*GetUniqueId)(ncclUniqueId *);
+  ncclResult_t (*CommInitRank)(ncclComm_t *, int, ncclUniqueId, int);
+  ncclResult_t (*CommDestroy)(ncclComm_t);
+  ncclResult_t (*AllGather)(const void *, void *, size_t, ncclDataType_t, ncclComm_t, cudaStream_t);
+  const char *(*GetErrorString)(ncclResult_t);
+  bool ok;
+};
+
+static const NcclApi &nccl()
+{
+  static NcclApi api = [] {
+    NcclApi a{};
+    void *h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_NOLOAD);     // the copy already in the process
+    if (!h) h = dlopen("libnccl.so.2", RTLD_NOW);
+    if (!h) h = dlopen("libnccl.so", RTLD_NOW);
+    if (!h) return a;
+    a.GetUniqueId = (decltype(a.GetUniqueId))dlsym(h, "ncclGetUniqueId");
+    a.CommInitRank = (decltype(a.CommInitRank))dlsym(h, "ncclCommInitRank");
+    a.CommDestroy = (decltype(a.CommDestroy))dlsym(h, "ncclCommDestroy");
+    a.AllGather = (decltype(a.AllGather))dlsym(h, "ncclAllGather");
+    a.GetErrorString = (decltype(a.GetErrorString))dlsym(h, "ncclGetErrorString");
+    a.ok = a.GetUniqueId && a.CommInitRank && a.CommDestroy && a.AllGather;
+    return a;
+  }();
+  return api;
+}
+
+// ---- merge kernels: G records per channel -> global statistics and coefficients ---------------
+// gathered: [world][C] float4.  One thread per channel; every rank computes the same thing.
+__global__ void sync_merge_fwd_kernel(FusedArgs a, const float4 *gathered, uint32_t world)
+{
+  const uint32_t c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= a.plan.C) return;
+  double sn = 0.0, sm = 0.0;
+  for (uint32_t r = 0; r < world; ++r) {
+    const float4 p = gathered[(size_t)r * a.plan.C + c];
+    sn += (double)p.x; sm += (double)p.x * (double)p.y;
+  }
+  const double mean = sm / sn;
+  double sq = 0.0;
+  for (uint32_t r = 0; r < world; ++r) {
+    const float4 p = gathered[(size_t)r * a.plan.C + c];
+    const double d = (double)p.y - mean;
+    sq += (double)p.z + (double)p.x * d * d;
+  }
+  a.mode = MODE_APPLY;          // makes finish_channel_fwd write outputs and coefficients
+  a.use_rec = 0;
+  finish_channel_fwd(a, c, sn, mean, sq);
+}
+
+__global__ void sync_merge_bwd_kernel(FusedArgs a, const float4 *gathered, uint32_t world)
+{
+  const uint32_t c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= a.plan.C) return;
+  double s1 = 0.0, s2 = 0.0;
+  for (uint32_t r = 0; r < world; ++r) {
+    const float4 p = gathered[(size_t)r * a.plan.C + c];
+    s1 += (double)p.x; s2 += (double)p.y;
+  }
+  a.mode = MODE_APPLY;
+  a.use_rec = 0;
+  finish_channel_bwd(a, c, s1, s2);
+}
+
+static size_t gather_bytes(uint32_t C, uint32_t world) { return (size_t)align_up_u64((uint64_t)16 * C * world, 256); }
+
+static int run_sync(FusedArgs &a, int dir, bool aligned, AnodeSyncComm *comm, size_t fused_ws_bytes, cudaStream_t stream)
+{
+  const NcclApi &api = nccl();
+  if (!comm || !api.ok) return ANODE_E_COMM;
+  // the gather buffer sits behind the single-GPU workspace
+  float4 *gathered = reinterpret_cast<float4 *>(a.ws + fused_ws_bytes);
+  const Plan base = a.plan;
+  a.mode = MODE_STATS;
+  int rc = launch_best(a, dir, aligned, stream);
+  if (rc) return rc;
+  const float4 *local = reinterpret_cast<const float4 *>(a.ws + a.plan.off_local);
+  if (api.AllGather(local, gathered, (size_t)4 * a.plan.C, ncclFloat, comm->nccl, stream) != ncclSuccess) return ANODE_E_COMM;
+  FusedArgs m = a;
+  const uint32_t threads = 128, blocks = (a.plan.C + threads - 1) / threads;
+  if (dir == 0) sync_merge_fwd_kernel<<<blocks, threads, 0, stream>>>(m, gathered, (uint32_t)comm->world);
+  else sync_merge_bwd_kernel<<<blocks, threads, 0, stream>>>(m, gathered, (uint32_t)comm->world);
+  if (cudaGetLastError() != cudaSuccess) return ANODE_E_LAUNCH;
+  a.plan = base;
+  a.mode = MODE_APPLY;
+  return launch_best(a, dir, aligned, stream);
+}
+
+}  // namespace anode_b200
+
+using namespace anode_b200;
+
+extern "C" size_t anode_gpu_sync_unique_id_bytes(void) { return sizeof(ncclUniqueId); }
+
+extern "C" int anode_gpu_sync_get_unique_id(void *out)
+{
+  const NcclApi &api = nccl();
+  if (!out) return ANODE_E_NULL;
+  if (!api.ok) return ANODE_E_COMM;
+  ncclUniqueId id;
+  if (api.GetUniqueId(&id) != ncclSuccess) return ANODE_E_COMM;
+  memcpy(out, &id, sizeof(id));
+  return ANODE_OK;
+}
+
+extern "C" int anode_gpu_sync_comm_create(const void *unique_id, int rank, int world, struct AnodeSyncComm **out)
+{
+  const NcclApi &api = nccl();
+  if (!unique_id || !out) return ANODE_E_NULL;
+  if (!api.ok || world < 1 || rank < 0 || rank >= world) return ANODE_E_COMM;
+  ncclUniqueId id;
+  memcpy(&id, unique_id, sizeof(id));
+  AnodeSyncComm *c = new AnodeSyncComm{};
+  c->rank = rank; c->world = world;
+  if (api.CommInitRank(&c->nccl, world, id, rank) != ncclSuccess) { delete c; return ANODE_E_COMM; }
+  *out = c;
+  return ANODE_OK;
+}
+
+extern "C" int anode_gpu_sync_comm_destroy(struct AnodeSyncComm *comm)
+{
+  if (!comm) return ANODE_E_NULL;
+  const NcclApi &api = nccl();
+  if (api.ok && comm->nccl) api.CommDestroy(comm->nccl);
+  delete comm;
+  return ANODE_OK;
+}
+
+extern "C" size_t anode_gpu_sync_batch_norm_workspace_bytes(uint32_t dim0, uint32_t dim1, uint32_t dim2, int world)
+{
+  const size_t base = anode_gpu_batch_norm_fused_workspace_bytes(dim0, dim1, dim2);
+  if (base == 0 || world < 1) return 0;
+  return base + gather_bytes(dim1, (uint32_t)world);
+}
+
+extern "C" int anode_gpu_sync_batch_norm_relu_fwd_3d1_packed_f32(
+    uint32_t dim0, uint32_t dim1, uint32_t dim2, float epsilon, float avg_rate, int relu,
+    const float *x, const float *gamma, const float *beta,
+    float *y, float *mean, float *var, float *run_mean, float *run_var,
+    struct AnodeSyncComm *comm, void *workspace, size_t workspace_bytes,
+    const struct KernelConfig *cfg, struct CUstream_st *stream)
+{
+  (void)cfg;
+  if (!comm) return ANODE_E_COMM;
+  const size_t fused = anode_gpu_batch_norm_fused_workspace_bytes(dim0, dim1, dim2);
+  if (fused == 0) return ANODE_E_DIMS;
+  if (workspace_bytes < fused + gather_bytes(dim1, (uint32_t)comm->world)) return ANODE_E_WORKSPACE;
+  FusedArgs a;
+  const int rc = prepare_fwd(a, dim0, dim1, dim2, epsilon, avg_rate, relu, x, gamma, beta, y, mean, var,
+                             run_mean, run_var, workspace, fused);
+  if (rc) return rc;
+  return run_sync(a, 0, aligned16(x) && aligned16(y), comm, fused, stream);
+}
+
+extern "C" int anode_gpu_sync_batch_norm_relu_bwd_3d1_packed_f32(
+    uint32_t dim0, uint32_t dim1, uint32_t dim2, uint64_t global_count, int relu, int accumulate,
+    const float *dy, const float *x, const float *mean, const float *var,
+    const float *gamma, const float *beta, float *dx, float *dgamma, float *dbeta,
+    struct AnodeSyncComm *comm, void *workspace, size_t workspace_bytes,
+    const struct KernelConfig *cfg, struct CUstream_st *stream)
+{
+  (void)cfg;
+  if (!comm) return ANODE_E_COMM;
+  const size_t fused = anode_gpu_batch_norm_fused_workspace_bytes(dim0, dim1, dim2);
+  if (fused == 0 || global_count < (uint64_t)dim0 * dim2) return ANODE_E_DIMS;
+  if (workspace_bytes < fused + gather_bytes(dim1, (uint32_t)comm->world)) return ANODE_E_WORKSPACE;
+  FusedArgs a;
+  const int rc = prepare_bwd(a, dim0, dim1, dim2, relu, accumulate, dy, x, mean, var, gamma, beta, dx,
+                             dgamma, dbeta, workspace, fused);
+  if (rc) return rc;
+  a.count_total = (double)global_count;
+  return run_sync(a, 1, aligned16(x) && aligned16(dy) && aligned16(dx), comm, fused, stream);
+}

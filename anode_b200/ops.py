@@ -415,3 +415,63 @@ class FusedBatchNormRelu:
                                          self.dgamma, self.dbeta, self.relu, WriteCap.Assign,
                                          self._workspace(x))
         return dx
+
+
+class SyncWorkspace(Workspace):
+    """Workspace of the synchronized entry points (single-GPU scratch + the gather buffer)."""
+
+    def __init__(self, dim0, dim1, dim2, world, device):
+        lib = _lib.load()
+        self.bytes = int(lib.anode_gpu_sync_batch_norm_workspace_bytes(dim0, dim1, dim2, world))
+        if self.bytes == 0:
+            raise AnodeError(-2, "anode_gpu_sync_batch_norm_workspace_bytes")
+        self.buf = torch.empty(self.bytes, dtype=torch.uint8, device=device)
+        check(lib.anode_gpu_batch_norm_fused_workspace_init(
+            ctypes.c_void_p(self.buf.data_ptr()), self.bytes, _stream(None)), "workspace_init")
+        self.key = (dim0, dim1, dim2, world)
+
+
+class SyncBatchNormRelu(FusedBatchNormRelu):
+    """FusedBatchNormRelu over a batch sharded across the ranks of `comm` (anode_b200.sync.SyncComm):
+    statistics, running averages, dgamma and dbeta are those of the global batch."""
+
+    launches_per_step = 6      # per direction: reduce kernel, merge kernel, apply kernel (+ one NCCL all-gather)
+
+    def __init__(self, channels, comm=None, global_count=None, **kw):
+        super().__init__(channels, **kw)
+        if comm is None:
+            from .sync import SyncComm
+            comm = SyncComm.from_torch_distributed()
+        self.comm = comm
+        self.global_count = global_count      # elements per channel over all ranks; default: equal shards
+
+    def _workspace(self, x):
+        key = dims_of(x) + (self.comm.world,)
+        if self._ws is None or self._ws.key != key:
+            self._ws = SyncWorkspace(*key, x.device)
+        return self._ws
+
+    def forward(self, x, out=None):
+        d0, c, n = dims_of(x)
+        y = out if out is not None else torch.empty_like(x)
+        ws = self._workspace(x)
+        check(_lib.load().anode_gpu_sync_batch_norm_relu_fwd_3d1_packed_f32(
+            d0, c, n, ctypes.c_float(self.epsilon), ctypes.c_float(self.avg_rate), int(self.relu),
+            _p(x), _p(self.gamma), _p(self.beta), _p(y), _p(self.mean), _p(self.var), _p(self.avg_mean),
+            _p(self.avg_var), self.comm.handle, ws.ptr, ws.bytes, _cfg(None), _stream(None)),
+            "anode_gpu_sync_batch_norm_relu_fwd_3d1_packed_f32")
+        self._x = x
+        return y
+
+    def backward(self, dy, out=None):
+        x = self._x
+        d0, c, n = dims_of(x)
+        dx = out if out is not None else torch.empty_like(x)
+        ws = self._workspace(x)
+        total = self.global_count if self.global_count is not None else d0 * n * self.comm.world
+        check(_lib.load().anode_gpu_sync_batch_norm_relu_bwd_3d1_packed_f32(
+            d0, c, n, ctypes.c_uint64(total), int(self.relu), 0,
+            _p(dy), _p(x), _p(self.mean), _p(self.var), _p(self.gamma), _p(self.beta), _p(dx),
+            _p(self.dgamma), _p(self.dbeta), self.comm.handle, ws.ptr, ws.bytes, _cfg(None), _stream(None)),
+            "anode_gpu_sync_batch_norm_relu_bwd_3d1_packed_f32")
+        return dx

@@ -1,0 +1,81 @@
+"""Synchronized batch-norm across the GPUs of one node: host side.
+
+One process per GPU (torch.distributed is the plumbing: it carries the 128-byte NCCL unique
+id to the other ranks and nothing else; the per-step exchange is enqueued by the C ABI on the
+caller's stream).  The reference has no synchronized batch-norm; its data-parallel training
+keeps per-process statistics and all-reduces gradients through host memory
+(src/proc_mpi.rs:138-148, src/ops_gpu.rs:538-545).
+
+`shard_range` and `merge_moments` are plain host code (no GPU): the sharding rule of the
+benchmark and a numpy restatement of the device-side merge, used by the CPU tests of the
+multi-rank logic.
+"""
+import ctypes
+
+import numpy as np
+
+from . import _lib
+from ._lib import check
+
+
+def shard_range(extent, rank, world):
+    """[lo, hi) of `extent` items owned by `rank`: contiguous, sizes differing by at most one."""
+    if not (0 <= rank < world):
+        raise ValueError("rank %d outside world %d" % (rank, world))
+    base, rem = divmod(extent, world)
+    lo = rank * base + min(rank, rem)
+    return lo, lo + base + (1 if rank < rem else 0)
+
+
+def merge_moments(records):
+    """Merges per-rank (count, mean, M2) records, shape [world, C, 3], in rank order in float64,
+    exactly as the device merge does (two passes: weighted mean, then M2 about it).
+    Returns (count, mean, M2) per channel."""
+    r = np.asarray(records, dtype=np.float64)
+    n = r[:, :, 0].sum(axis=0)
+    mean = (r[:, :, 0] * r[:, :, 1]).sum(axis=0) / n
+    d = r[:, :, 1] - mean[None, :]
+    m2 = (r[:, :, 2] + r[:, :, 0] * d * d).sum(axis=0)
+    return n, mean, m2
+
+
+def local_moments(x):
+    """(count, mean, M2) per channel of a local shard [N, C, *spatial] (float64, host)."""
+    x64 = np.asarray(x, dtype=np.float64)
+    ax = (0,) + tuple(range(2, x64.ndim))
+    n = np.full(x64.shape[1], x64.size / x64.shape[1])
+    mean = x64.mean(axis=ax)
+    bs = (1, -1) + (1,) * (x64.ndim - 2)
+    m2 = ((x64 - mean.reshape(bs)) ** 2).sum(axis=ax)
+    return np.stack([n, mean, m2], axis=1)
+
+
+class SyncComm:
+    """Communicator of the synchronized entry points (wraps AnodeSyncComm of the C ABI)."""
+
+    def __init__(self, handle, rank, world):
+        self.handle, self.rank, self.world = handle, rank, world
+
+    @classmethod
+    def from_torch_distributed(cls, group=None):
+        """Collective over `group`: rank 0 creates the unique id, torch.distributed broadcasts it,
+        every rank builds its communicator on its current CUDA device."""
+        import torch
+        import torch.distributed as dist
+        lib = _lib.load()
+        rank, world = dist.get_rank(group), dist.get_world_size(group)
+        nbytes = int(lib.anode_gpu_sync_unique_id_bytes())
+        buf = (ctypes.c_ubyte * nbytes)()
+        if rank == 0:
+            check(lib.anode_gpu_sync_get_unique_id(buf), "anode_gpu_sync_get_unique_id")
+        t = torch.tensor(list(buf), dtype=torch.uint8, device="cuda" if dist.get_backend(group) == "nccl" else "cpu")
+        dist.broadcast(t, src=dist.get_global_rank(group, 0) if group is not None else 0, group=group)
+        raw = bytes(t.cpu().tolist())
+        handle = ctypes.c_void_p()
+        check(lib.anode_gpu_sync_comm_create(raw, rank, world, ctypes.byref(handle)), "anode_gpu_sync_comm_create")
+        return cls(handle, rank, world)
+
+    def destroy(self):
+        if self.handle:
+            _lib.load().anode_gpu_sync_comm_destroy(self.handle)
+            self.handle = None

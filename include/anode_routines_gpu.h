@@ -226,6 +226,50 @@ int anode_gpu_online_average_f32(
     uint32_t len, float rate, const float *x, float *y,
     const struct KernelConfig *cfg, struct CUstream_st *stream);
 
+/* ===================================================================================
+ * 3. Synchronized batch-norm over the GPUs of one node (new).
+ *
+ * Every rank holds a shard of the batch (or a spatial slab) with all dim1 channels; statistics
+ * and the backward sums are taken over all shards.  The reference has no counterpart: its
+ * batch-norm is per process, and its one collective is the host-staged MPI allreduce of
+ * gradients (src/proc_mpi.rs:138-148 called from SumSpmdOp, src/ops_gpu.rs:538-545), whose
+ * role for this path the exchange below takes over, on the device, over NVLink.
+ *
+ * One process per GPU.  Rank 0 obtains a unique id, distributes it by any means (128 bytes),
+ * and every rank creates its communicator with the CUDA device it will use made current.
+ * Calls on a communicator are collective: every rank makes the same sequence of calls.
+ * =================================================================================== */
+struct AnodeSyncComm;
+
+size_t anode_gpu_sync_unique_id_bytes(void);
+int anode_gpu_sync_get_unique_id(void *out);
+int anode_gpu_sync_comm_create(const void *unique_id, int rank, int world, struct AnodeSyncComm **out);
+int anode_gpu_sync_comm_destroy(struct AnodeSyncComm *comm);
+
+/* Scratch for a LOCAL [dim0, dim1, dim2] shard when `world` ranks take part. */
+size_t anode_gpu_sync_batch_norm_workspace_bytes(uint32_t dim0, uint32_t dim1, uint32_t dim2, int world);
+
+/* Forward: as anode_gpu_batch_norm_relu_fused_fwd_3d1_packed_f32, with mean / var / running
+ * statistics over the global batch (every rank receives the same values). */
+int anode_gpu_sync_batch_norm_relu_fwd_3d1_packed_f32(
+    uint32_t dim0, uint32_t dim1, uint32_t dim2,
+    float epsilon, float avg_rate, int relu,
+    const float *x, const float *gamma, const float *beta,
+    float *y, float *mean, float *var, float *run_mean, float *run_var,
+    struct AnodeSyncComm *comm, void *workspace, size_t workspace_bytes,
+    const struct KernelConfig *cfg, struct CUstream_st *stream);
+
+/* Backward: as anode_gpu_batch_norm_relu_fused_bwd_3d1_packed_f32; dgamma / dbeta are the
+ * global sums (identical on every rank) and `global_count` is the number of elements per
+ * channel over all ranks (the M of the formulas). */
+int anode_gpu_sync_batch_norm_relu_bwd_3d1_packed_f32(
+    uint32_t dim0, uint32_t dim1, uint32_t dim2, uint64_t global_count, int relu, int accumulate,
+    const float *dy, const float *x, const float *mean, const float *var,
+    const float *gamma, const float *beta,
+    float *dx, float *dgamma, float *dbeta,
+    struct AnodeSyncComm *comm, void *workspace, size_t workspace_bytes,
+    const struct KernelConfig *cfg, struct CUstream_st *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,78 @@
+"""Synchronized batch-norm on real GPUs through the C ABI.  world = 1 runs everywhere; the
+2-rank case needs two visible GPUs (one process per GPU, NCCL) and is skipped otherwise.
+Parity definition: the G-way result equals the oracle on the concatenated global batch."""
+import os
+import sys
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from oracle import bn_oracle as o
+from tests.util import check_layer, make_inputs
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _worker(rank, world, port, shape, axis, out_dir, dist_kind):
+    sys.path.insert(0, ROOT)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    from anode_b200 import ops, sync
+    d = make_inputs(shape, seed=41, dist=dist_kind, loc=0.5 if dist_kind == "normal" else 0.0,
+                    scale=2.0 if dist_kind == "normal" else 4.0)
+    lo, hi = sync.shard_range(shape[axis], rank, world)
+    idx = [slice(None)] * len(shape); idx[axis] = slice(lo, hi)
+    x = torch.from_numpy(np.ascontiguousarray(d["x"][tuple(idx)])).cuda()
+    dy = torch.from_numpy(np.ascontiguousarray(d["dy"][tuple(idx)])).cuda()
+    layer = ops.SyncBatchNormRelu(shape[1], epsilon=1e-5, avg_rate=0.1)
+    layer.gamma.copy_(torch.from_numpy(d["gamma"])); layer.beta.copy_(torch.from_numpy(d["beta"]))
+    for _ in range(2):                      # twice: the workspace must come back clean
+        layer.avg_mean.zero_(); layer.avg_var.fill_(1.0)
+        y = layer.forward(x)
+        dx = layer.backward(dy)
+    torch.cuda.synchronize()
+    assert layer.status() == 0
+    np.savez(os.path.join(out_dir, "r%d.npz" % rank), y=y.cpu().numpy(), dx=dx.cpu().numpy(),
+             mean=layer.mean.cpu().numpy(), var=layer.var.cpu().numpy(), run_mean=layer.avg_mean.cpu().numpy(),
+             run_var=layer.avg_var.cpu().numpy(), dgamma=layer.dgamma.cpu().numpy(), dbeta=layer.dbeta.cpu().numpy())
+    dist.barrier()
+    layer.comm.destroy()
+    dist.destroy_process_group()
+
+
+CASES = [((16, 8, 28, 28), 0, "normal"), ((8, 4, 8, 16, 16), 2, "normal"), ((32, 64, 7, 7), 0, "student3"),
+         ((6, 3, 5, 5), 0, "normal")]
+
+
+def _run(tmp_path, world, shape, axis, dist_kind):
+    port = 30000 + (os.getpid() * 7 + hash((shape, axis, world)) % 997) % 3000
+    mp.spawn(_worker, args=(world, port, shape, axis, str(tmp_path), dist_kind), nprocs=world, join=True)
+    d = make_inputs(shape, seed=41, dist=dist_kind, loc=0.5 if dist_kind == "normal" else 0.0,
+                    scale=2.0 if dist_kind == "normal" else 4.0)
+    truth = o.bn_relu_fwd_bwd_f64(d["x"], d["dy"], 1e-5, 0.1, d["run_mean"], d["run_var"], d["gamma"], d["beta"])
+    parts = [np.load(os.path.join(str(tmp_path), "r%d.npz" % r)) for r in range(world)]
+    got = {k: parts[0][k] for k in ("mean", "var", "run_mean", "run_var", "dgamma", "dbeta")}
+    for p in parts[1:]:
+        for k in got:
+            assert (p[k] == got[k]).all(), k      # identical on every rank, bit for bit
+    got["y"] = np.concatenate([p["y"] for p in parts], axis=axis)
+    got["dx"] = np.concatenate([p["dx"] for p in parts], axis=axis)
+    check_layer(got, truth, d["x"], d["gamma"], d["beta"], "world %d " % world)
+
+
+@pytest.mark.parametrize("shape,axis,dist_kind", CASES)
+def test_sync_world1_matches_oracle(tmp_path, shape, axis, dist_kind):
+    _run(tmp_path, 1, shape, axis, dist_kind)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+@pytest.mark.parametrize("shape,axis,dist_kind", CASES)
+def test_sync_world2_matches_oracle(tmp_path, shape, axis, dist_kind):
+    _run(tmp_path, 2, shape, axis, dist_kind)
