@@ -51,6 +51,8 @@ SIGNATURES = {
         (c_int, _D + [f32, f32, c_int] + [vp] * 8 + [vp, size_t] + _T),
     "anode_gpu_batch_norm_relu_fused_bwd_3d1_packed_f32":
         (c_int, _D + [c_int, c_int] + [vp] * 9 + [vp, size_t] + _T),
+    "anode_gpu_batch_norm_relu_fused_fwd_static_3d1_packed_f32":
+        (c_int, _D + [f32, f32, c_int] + [vp] * 8 + _T),
     "anode_gpu_online_average_f32": (c_int, [u32, f32, vp, vp] + _T),
     "anode_gpu_sync_unique_id_bytes": (size_t, []),
     "anode_gpu_sync_get_unique_id": (c_int, [vp]),
@@ -94,6 +96,7 @@ ERRORS = {
     -4: "ANODE_E_LAUNCH: the CUDA runtime refused the launch",
     -5: "ANODE_E_COMM: communicator missing, inconsistent, or NCCL failure",
     -6: "ANODE_E_ALIGN: tensor pointers must be 4-byte aligned",
+    -7: "ANODE_E_TOO_LARGE: the problem needs more scratch than the library's built-in array holds",
 }
 
 

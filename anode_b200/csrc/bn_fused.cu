@@ -139,6 +139,18 @@ int launch_ring(FusedArgs &a, const RingGeom &g, int dir, cudaStream_t stream)
   return ANODE_OK;
 }
 
+// Bytes at the start of a workspace that hold progress counters, flags and records, i.e. what has
+// to be zero when a launch begins (the per-tile partials behind them are written before they are read).
+uint64_t control_region_bytes(uint32_t dim0, uint32_t C, uint32_t N, bool aligned)
+{
+  uint64_t n = plan_for(dim0, C, N, aligned).off_part;
+  for (int dir = 0; dir < 2; ++dir) {
+    Plan rp; RingGeom g;
+    if (ring_plan_for(dim0, C, N, aligned, dir, rp, g) && rp.off_part > n) n = rp.off_part;
+  }
+  return n;
+}
+
 // Launches direction `dir` of a prepared call with the best kernel that applies.
 int launch_best(FusedArgs &a, int dir, bool aligned, cudaStream_t stream)
 {

@@ -172,6 +172,7 @@ void anode_gpu_positive_clip_flat_map_bwd_f32(
 #define ANODE_E_LAUNCH     -4   /* the CUDA runtime refused the launch */
 #define ANODE_E_COMM       -5   /* communicator missing / inconsistent / NCCL failure */
 #define ANODE_E_ALIGN      -6   /* tensor pointers must be 4-byte aligned */
+#define ANODE_E_TOO_LARGE  -7   /* the problem needs more scratch than the library's built-in array holds */
 
 /* Bits of the device status word. */
 #define ANODE_ST_WAIT_STATS   1u  /* a wait for a channel's statistics ran out */
@@ -218,6 +219,28 @@ int anode_gpu_batch_norm_relu_fused_bwd_3d1_packed_f32(
     const float *gamma, const float *beta,
     float *dx, float *dgamma, float *dbeta,
     void *workspace, size_t workspace_bytes,
+    const struct KernelConfig *cfg, struct CUstream_st *stream);
+
+/* Forward pass for callers that have no scratch memory to give.  No counterpart in the
+ * reference.  Same arguments and results as anode_gpu_batch_norm_relu_fused_fwd_3d1_packed_f32
+ * minus the workspace: anode's op closures pass only dimensions, inputs, pre-made outputs, a
+ * launch hint and a stream (src/ops_gpu.rs:3763-3771), and code inside a memory-pool transaction
+ * must not call cudaMalloc (it synchronises the device), so neither can provide a workspace.
+ * The scratch is a fixed array of ANODE_STATIC_SCRATCH_BYTES inside the library, held on every GPU
+ * that loads it until the process exits; this call allocates and frees nothing.
+ *   - Problems whose scratch need (anode_gpu_batch_norm_fused_workspace_bytes gives an upper
+ *     bound) exceeds the array return ANODE_E_TOO_LARGE and enqueue nothing.
+ *   - All calls on a device share the array, which keeps the previous call's contents; every call
+ *     first clears, on `stream`, the part that has to start at zero.  Calls that may overlap on
+ *     the GPU (different streams without an ordering between them) race on it: serialise them.
+ *   - The first call on each device looks up the array's device address; make that first call
+ *     with the device current and outside of any stream capture. */
+#define ANODE_STATIC_SCRATCH_BYTES (4u << 20)
+int anode_gpu_batch_norm_relu_fused_fwd_static_3d1_packed_f32(
+    uint32_t dim0, uint32_t dim1, uint32_t dim2,
+    float epsilon, float avg_rate, int relu,
+    const float *x, const float *gamma, const float *beta,
+    float *y, float *mean, float *var, float *run_mean, float *run_var,
     const struct KernelConfig *cfg, struct CUstream_st *stream);
 
 /* Running-statistic update on its own (OnlineAverageOp, src/ops_gpu.rs:6034-6077; rule
