@@ -46,7 +46,7 @@ struct Plan {
   uint32_t lookahead_steps; // distance, in steps, between reducing and applying a tile
   uint32_t div_mul;         // floor(2^32 / (piece_len/vec)) + 1, see fast_div; 0 when piece_len/vec == 1
   // workspace offsets, in bytes from the workspace base
-  uint32_t off_done, off_ready, off_applied, off_coef, off_rec, off_local, off_part;
+  uint32_t off_done, off_ready, off_applied, off_coef, off_rec, off_local, off_tag, off_part;
   uint64_t ws_bytes;
 };
 
@@ -170,6 +170,8 @@ inline Plan make_plan(uint32_t dim0, uint32_t C, uint32_t N, bool aligned16,
   p.off_coef = (uint32_t)off;    off = align_up_u64(off + 32ull * C, 256);   // 8 floats / channel
   p.off_rec = (uint32_t)off;     off = align_up_u64(off + 8ull * C, 256);    // one tagged 64-bit record / channel
   p.off_local = (uint32_t)off;   off = align_up_u64(off + 16ull * C, 256);   // 4 floats / channel
+  // two buffers of one tagged 64-bit partial per tile (used alternately, launch by launch)
+  p.off_tag = (uint32_t)off;     off = align_up_u64(off + 16ull * p.total_tiles * p.cb, 256);
   p.off_part = (uint32_t)off;    off = align_up_u64(off + 16ull * p.total_tiles * p.cb, 256);
   p.ws_bytes = off;
   return p;

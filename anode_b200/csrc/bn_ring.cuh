@@ -25,7 +25,10 @@
 
 namespace anode_b200 {
 
-constexpr uint32_t kConsumers = 256;
+#ifndef ANODE_RING_CONSUMERS
+#define ANODE_RING_CONSUMERS 512
+#endif
+constexpr uint32_t kConsumers = ANODE_RING_CONSUMERS;   // consumer threads (a power of two, 256..1024)
 constexpr uint32_t kRingThreads = kConsumers + 96;   // + producer, delivery and coefficient warps
 constexpr uint32_t kResQ = 4;                        // partial mailbox depth
 constexpr uint32_t kCoefQ = 4;                       // coefficient mailbox depth
@@ -55,6 +58,7 @@ struct RingCtl {
   float mom[3 * (kConsumers / 32)];
   volatile uint32_t abort;
   uint32_t last_block;
+  uint32_t parity;       // which of the two tagged-partial buffers this launch uses
 };
 
 // ---- mbarrier / bulk-copy primitives --------------------------------------------------------
@@ -224,36 +228,52 @@ __device__ __forceinline__ float4 *coef_box(unsigned char *sm, const RingGeom &g
 // ======================================================================================
 // ---- regime R: each consumer warp handles vectors warp*32 + lane + i*256 of the tile ----------
 constexpr uint32_t kCWarps = kConsumers / 32;
+constexpr uint32_t kPerTurn = 32 / kCWarps;      // mailbox entries the delivery warp merges per turn
+
+// 128-bit shared load by 32-bit shared address (keeps the address arithmetic in 32 bits)
+__device__ __forceinline__ Pack<4> lds128(uint32_t saddr)
+{
+  Pack<4> r;
+  asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(r.v[0]), "=f"(r.v[1]), "=f"(r.v[2]), "=f"(r.v[3]) : "r"(saddr) : "memory");
+  return r;
+}
+constexpr uint32_t kVecStride = kConsumers * 16;     // bytes between consecutive vectors of one thread
 
 template <int DIR>
 __device__ __forceinline__ void warp_reduce_R(const FusedArgs &a, const RingGeom &g, unsigned char *sm, RingCtl *ctl,
                                               const TileRange &tr, uint32_t slot, float4 *res)
 {
   const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const float *xs = slot_x(sm, g, slot);
   const uint32_t nvec = (tr.len / 4) * tr.rows;        // the slot holds the tile's rows back to back
+  const uint32_t cnt = tid < nvec ? (nvec - tid + kConsumers - 1) / kConsumers : 0;   // this thread's vectors
+  uint32_t ax = smem_u32(slot_x(sm, g, slot)) + tid * 16;
   if constexpr (DIR == 0) {
-    // shifted sums: K is this thread's first element (see bn_fused.cuh)
+    // shifted sums: K is this thread's first element (see bn_fused.cuh); two accumulator pairs
     float K = 0.f;
-    if (tid < nvec) K = xs[4 * tid];
-    float s = 0.f, q = 0.f;
-    for (uint32_t j0 = tid; j0 < nvec; j0 += kConsumers * kUnroll) {
-      Pack<4> v[kUnroll];
+    if (cnt) K = lds128(ax).v[0];
+    float s0 = 0.f, q0 = 0.f, s1 = 0.f, q1 = 0.f;
+    uint32_t i = 0;
+    for (; i + 4 <= cnt; i += 4, ax += 4 * kVecStride) {
+      const Pack<4> v0 = lds128(ax), v1 = lds128(ax + kVecStride), v2 = lds128(ax + 2 * kVecStride), v3 = lds128(ax + 3 * kVecStride);
 #pragma unroll
-      for (int u = 0; u < kUnroll; ++u) {
-        const uint32_t j = j0 + u * kConsumers;
-        v[u] = (j < nvec) ? lds4(xs + 4 * (size_t)j) : pack_fill<4>(K);
+      for (int e = 0; e < 4; ++e) {
+        const float d0 = v0.v[e] - K, d1 = v1.v[e] - K, d2 = v2.v[e] - K, d3 = v3.v[e] - K;
+        s0 += d0; q0 = fmaf(d0, d0, q0); s1 += d1; q1 = fmaf(d1, d1, q1);
+        s0 += d2; q0 = fmaf(d2, d2, q0); s1 += d3; q1 = fmaf(d3, d3, q1);
       }
+    }
+    for (; i < cnt; ++i, ax += kVecStride) {
+      const Pack<4> v0 = lds128(ax);
 #pragma unroll
-      for (int u = 0; u < kUnroll; ++u)
-#pragma unroll
-        for (int i = 0; i < 4; ++i) { const float d = v[u].v[i] - K; s += d; q = fmaf(d, d, q); }
+      for (int e = 0; e < 4; ++e) { const float d0 = v0.v[e] - K; s0 += d0; q0 = fmaf(d0, d0, q0); }
     }
     __syncwarp();
     if (lane == 0) mbar_arrive(&ctl->empty[slot]);
+    const float s = s0 + s1, q = q0 + q1;
     Moments m{0.f, 0.f, 0.f};
-    if (tid < nvec) {
-      m.n = (float)(((nvec - tid + kConsumers - 1) / kConsumers) * 4);
+    if (cnt) {
+      m.n = (float)(cnt * 4);
       const float inv = __fdividef(1.0f, m.n);
       m.mean = fmaf(s, inv, K);
       m.m2 = fmaxf(q - s * s * inv, 0.f);
@@ -261,32 +281,37 @@ __device__ __forceinline__ void warp_reduce_R(const FusedArgs &a, const RingGeom
     m = warp_merge(m);
     if (lane == 0) res[warp] = make_float4(m.n, m.mean, m.m2, 0.f);
   } else {
-    const float *ds = slot_dy<1>(sm, g, slot);
+    uint32_t ad = ax + g.slot_floats * 4;
     const float4 cf = slot_side<1>(sm, g, slot)[0];
     const float mean = cf.x, scale = cf.y, beta = cf.z;
     const bool relu = a.relu != 0;
-    float s1 = 0.f, s2 = 0.f;
-    for (uint32_t j0 = tid; j0 < nvec; j0 += kConsumers * kUnroll) {
-      Pack<4> vx[kUnroll], vd[kUnroll];
+    float s1 = 0.f, s2 = 0.f, t1 = 0.f, t2 = 0.f;
+    uint32_t i = 0;
+    for (; i + 2 <= cnt; i += 2, ax += 2 * kVecStride, ad += 2 * kVecStride) {
+      const Pack<4> x0 = lds128(ax), x1 = lds128(ax + kVecStride), g0 = lds128(ad), g1 = lds128(ad + kVecStride);
 #pragma unroll
-      for (int u = 0; u < kUnroll; ++u) {
-        const uint32_t j = j0 + u * kConsumers;
-        if (j < nvec) { vx[u] = lds4(xs + 4 * (size_t)j); vd[u] = lds4(ds + 4 * (size_t)j); }
-        else { vx[u] = pack_fill<4>(mean); vd[u] = pack_fill<4>(0.f); }
+      for (int e = 0; e < 4; ++e) {
+        const float d0 = x0.v[e] - mean, d1 = x1.v[e] - mean;
+        const float y0 = fmaf(d0, scale, beta), y1 = fmaf(d1, scale, beta);
+        // dz = dy * (float)(y > 0)  (routines_gpu/flat_map.cu:191-192)
+        const float z0 = relu ? g0.v[e] * (y0 > 0.0f ? 1.0f : 0.0f) : g0.v[e];
+        const float z1 = relu ? g1.v[e] * (y1 > 0.0f ? 1.0f : 0.0f) : g1.v[e];
+        s1 += z0; s2 = fmaf(z0, d0, s2); t1 += z1; t2 = fmaf(z1, d1, t2);
       }
+    }
+    for (; i < cnt; ++i, ax += kVecStride, ad += kVecStride) {
+      const Pack<4> x0 = lds128(ax), g0 = lds128(ad);
 #pragma unroll
-      for (int u = 0; u < kUnroll; ++u)
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const float d = vx[u].v[i] - mean;
-          const float yb = fmaf(d, scale, beta);
-          const float dz = relu ? vd[u].v[i] * (yb > 0.0f ? 1.0f : 0.0f) : vd[u].v[i];
-          s1 += dz; s2 = fmaf(dz, d, s2);
-        }
+      for (int e = 0; e < 4; ++e) {
+        const float d0 = x0.v[e] - mean;
+        const float y0 = fmaf(d0, scale, beta);
+        const float z0 = relu ? g0.v[e] * (y0 > 0.0f ? 1.0f : 0.0f) : g0.v[e];
+        s1 += z0; s2 = fmaf(z0, d0, s2);
+      }
     }
     __syncwarp();
     if (lane == 0) mbar_arrive(&ctl->empty[slot]);
-    s1 = warp_sum(s1); s2 = warp_sum(s2);
+    s1 = warp_sum(s1 + t1); s2 = warp_sum(s2 + t2);
     if (lane == 0) res[warp] = make_float4(s1, s2, 0.f, 0.f);
   }
 }
@@ -296,8 +321,6 @@ __device__ __forceinline__ void warp_apply_R(const FusedArgs &a, const RingGeom 
                                              const TileRange &tr, uint32_t slot, const float4 *coef, uint32_t coef_q)
 {
   const uint32_t tid = threadIdx.x, lane = tid & 31;
-  const float *xs = slot_x(sm, g, slot);
-  const float *ds = slot_dy<DIR>(sm, g, slot);
   const bool relu = a.relu != 0, acc = a.accumulate != 0;
   const uint64_t drop = policy_drop();
   const uint64_t rs = (uint64_t)a.plan.C * a.plan.dim0;
@@ -305,34 +328,34 @@ __device__ __forceinline__ void warp_apply_R(const FusedArgs &a, const RingGeom 
   const float4 c0 = coef[0], c1 = coef[1];
   const float mean = c0.x, scale = c0.y, beta = c0.z, cB = c1.x, cC = c1.y;
   const uint32_t per_row = tr.len / 4, nvec = per_row * tr.rows;
+  const uint32_t cnt = tid < nvec ? (nvec - tid + kConsumers - 1) / kConsumers : 0;
   const uint32_t mul = a.plan.div_mul;       // rows > 1 only occurs with whole rows, where per_row matches it
-  for (uint32_t j0 = tid; j0 < nvec; j0 += kConsumers * kUnroll) {
+  const bool one_row = tr.rows == 1;
+  uint32_t ax = smem_u32(slot_x(sm, g, slot)) + tid * 16;
+  uint32_t ad = ax + g.slot_floats * 4;
+  uint32_t j = tid;
+  float *po = out + 4 * (size_t)tid;           // running output pointer of the single-row case
+  for (uint32_t i = 0; i < cnt; ++i, ax += kVecStride, ad += kVecStride, j += kConsumers, po += 4 * kConsumers) {
+    const Pack<4> vx = lds128(ax);
+    float *dst = po;
+    if (!one_row) { const uint32_t r = fast_div(j, mul); dst = out + (size_t)r * rs + 4 * (size_t)(j - r * per_row); }
+    Pack<4> o;
+    if constexpr (DIR == 0) {
 #pragma unroll
-    for (int u = 0; u < kUnroll; ++u) {
-      const uint32_t j = j0 + u * kConsumers;
-      if (j < nvec) {
-        const Pack<4> vx = lds4(xs + 4 * (size_t)j);
-        Pack<4> o;
-        size_t off = 4 * (size_t)j;
-        if (tr.rows != 1) { const uint32_t r = fast_div(j, mul); off = (size_t)r * rs + 4 * (size_t)(j - r * per_row); }
-        if constexpr (DIR == 0) {
+      for (int e = 0; e < 4; ++e) { const float yb = fmaf(vx.v[e] - mean, scale, beta); o.v[e] = relu ? positive_clip(yb) : yb; }
+    } else {
+      const Pack<4> vd = lds128(ad);
+      if (acc) o = Pack<4>::load(dst);
 #pragma unroll
-          for (int i = 0; i < 4; ++i) { const float yb = fmaf(vx.v[i] - mean, scale, beta); o.v[i] = relu ? positive_clip(yb) : yb; }
-        } else {
-          const Pack<4> vd = lds4(ds + 4 * (size_t)j);
-          if (acc) o = Pack<4>::load(out + off);
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const float d = vx.v[i] - mean;
-            const float yb = fmaf(d, scale, beta);
-            const float dz = relu ? vd.v[i] * (yb > 0.0f ? 1.0f : 0.0f) : vd.v[i];
-            const float dx = fmaf(scale, dz, fmaf(cB, d, cC));
-            o.v[i] = acc ? o.v[i] + dx : dx;
-          }
-        }
-        o.store(out + off, drop);
+      for (int e = 0; e < 4; ++e) {
+        const float d = vx.v[e] - mean;
+        const float yb = fmaf(d, scale, beta);
+        const float dz = relu ? vd.v[e] * (yb > 0.0f ? 1.0f : 0.0f) : vd.v[e];
+        const float dx = fmaf(scale, dz, fmaf(cB, d, cC));
+        o.v[e] = acc ? o.v[e] + dx : dx;
       }
     }
+    o.store(dst, drop);
   }
   __syncwarp();
   if (lane == 0) { mbar_arrive(&ctl->empty[slot]); mbar_arrive(&ctl->coef_empty[coef_q]); }
@@ -613,10 +636,133 @@ __device__ __forceinline__ void warp_finish_unit_S(const FusedArgs &a, uint32_t 
 }
 
 // ======================================================================================
+// fused mode, regime R: every block merges the partials of the units it applies itself
+// ======================================================================================
+// Instead of counting deliveries and electing a finisher, a delivery is a single 8-byte store of a
+// tagged partial -- forward (mean, M2), backward (sum dz, sum dz*(x-mean)), lowest mantissa bit of
+// the second value forced to one so the word is never all zero -- and whoever needs a unit polls
+// the unit's partial words until none is zero, then merges them in a fixed order in double
+// precision.  All blocks compute bit-identical coefficients; no atomics, fences or extra round
+// trips sit between the last delivery and the first apply.  The element count of a partial
+// follows from the tile geometry.  Two buffers are used alternately, launch by launch (parity
+// word in the workspace header): a delivery also zeroes its word in the other buffer.
+__device__ __forceinline__ unsigned long long *tag_buf(const FusedArgs &a, uint32_t parity)
+{
+  return reinterpret_cast<unsigned long long *>(a.ws + a.plan.off_tag) + (size_t)parity * a.plan.total_tiles * a.plan.cb;
+}
+__device__ __forceinline__ unsigned long long ld_relaxed_gpu_u64(const unsigned long long *p)
+{
+  unsigned long long v;
+  asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_relaxed_gpu_u64(unsigned long long *p, unsigned long long v)
+{
+  asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+constexpr int kPullRegs = 8;      // partial words per lane per round (256 tiles per round)
+
+// Whole warp.  Returns false when the wait ran out (abort raised).  On success c0 / c1 hold the
+// unit's coefficients in every lane; `owner` makes lane 0 write the per-channel outputs.
+template <int DIR>
+__device__ __forceinline__ bool pull_merge_unit(const FusedArgs &a, RingCtl *ctl, uint32_t *status, uint32_t u, bool owner,
+                                                float4 &c0, float4 &c1)
+{
+  const Plan &P = a.plan;
+  const uint32_t lane = threadIdx.x & 31, T = P.tiles_per_unit;
+  const unsigned long long *buf = tag_buf(a, ctl->parity) + (size_t)u * T;
+  // inputs that do not depend on the partials: fetch them while waiting
+  const float gm = a.gamma ? a.gamma[u] : 1.0f;
+  const float bt = (a.gamma && a.beta) ? a.beta[u] : 0.0f;
+  float mean_in = 0.f, var_in = 1.f;
+  if constexpr (DIR == 1) { mean_in = a.mean_in[u]; var_in = a.var_in[u]; }
+  Moments64 tot{0.0, 0.0, 0.0};
+  double s1 = 0.0, s2 = 0.0;
+  const long long t0 = clock64();
+  for (uint32_t k0 = 0; k0 < T; k0 += 32u * kPullRegs) {
+    unsigned long long r[kPullRegs];
+    for (;;) {
+      bool all = true;
+#pragma unroll
+      for (int i = 0; i < kPullRegs; ++i) {
+        const uint32_t k = k0 + lane + 32u * i;
+        r[i] = (k < T) ? ld_relaxed_gpu_u64(buf + k) : 1ull;
+        all = all && (r[i] != 0ull);
+      }
+      if (__all_sync(0xffffffffu, all)) break;
+      __nanosleep(100);
+      uint32_t stop = 0;
+      if (lane == 0) {
+        if (ctl->abort) stop = 1;
+        else if (clock64() - t0 > kWaitCycles) { atomicOr(status, ANODE_ST_WAIT_STATS); ctl->abort = 1; stop = 1; }
+      }
+      if (__shfl_sync(0xffffffffu, stop, 0)) return false;
+    }
+    if constexpr (DIR == 0) {
+      double nk[kPullRegs];
+      double sn = 0.0, sm = 0.0;
+#pragma unroll
+      for (int i = 0; i < kPullRegs; ++i) {
+        const uint32_t k = k0 + lane + 32u * i;
+        nk[i] = 0.0;
+        if (k < T) { const TileRange tr = tile_range(P, u * T + k); nk[i] = (double)tr.rows * (double)tr.len; }
+        const double mk = (double)__uint_as_float((uint32_t)(r[i] & 0xffffffffull));
+        sn += nk[i]; sm = fma(nk[i], mk, sm);
+      }
+      sn = warp_sum_all(sn); sm = warp_sum_all(sm);
+      const double mean = sm / sn;
+      double sq = 0.0;
+#pragma unroll
+      for (int i = 0; i < kPullRegs; ++i) {
+        const double mk = (double)__uint_as_float((uint32_t)(r[i] & 0xffffffffull));
+        const double m2 = (double)__uint_as_float((uint32_t)(r[i] >> 32));
+        const double d = mk - mean;
+        if (nk[i] > 0.0) sq += m2 + nk[i] * d * d;
+      }
+      sq = warp_sum_all(sq);
+      tot = merge64(tot, Moments64{sn, mean, sq});
+    } else {
+#pragma unroll
+      for (int i = 0; i < kPullRegs; ++i) {
+        const uint32_t k = k0 + lane + 32u * i;
+        if (k < T) {
+          s1 += (double)__uint_as_float((uint32_t)(r[i] & 0xffffffffull));
+          s2 += (double)__uint_as_float((uint32_t)(r[i] >> 32));
+        }
+      }
+    }
+  }
+  if constexpr (DIR == 0) {
+    const float mf = (float)tot.mean;
+    const float vf = (float)(tot.m2 / tot.n + (double)a.epsilon);     // biased, epsilon folded in (batch_norm.cu:160)
+    c0 = make_float4(mf, gm * inv_std(vf), bt, 0.f);
+    c1 = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (owner && lane == 0) {
+      a.mean[u] = mf; a.var[u] = vf;
+      if (a.run_mean) { const float o = a.run_mean[u]; a.run_mean[u] = o + a.avg_rate * (mf - o); }
+      if (a.run_var) { const float o = a.run_var[u]; a.run_var[u] = o + a.avg_rate * (vf - o); }
+    }
+  } else {
+    s1 = warp_sum_all(s1); s2 = warp_sum_all(s2);
+    const float r = inv_std(var_in);
+    const double rs2 = (double)r * s2;                       // sum(dz * xhat)
+    const double A = (double)gm * (double)r;
+    const double invM = 1.0 / a.count_total;
+    c0 = make_float4(mean_in, gm * r, bt, 0.f);
+    c1 = make_float4((float)(-A * (double)r * rs2 * invM), (float)(-A * s1 * invM), 0.f, 0.f);
+    if (owner && lane == 0) {
+      if (a.dbeta) a.dbeta[u] = (float)s1;
+      if (a.dgamma) a.dgamma[u] = (float)rs2;
+    }
+  }
+  return true;
+}
+
+// ======================================================================================
 // the kernel
 // ======================================================================================
 template <int DIR, int REGIME>
-__global__ void __launch_bounds__(kRingThreads, 2) bn_ring_kernel(const FusedArgs a, const RingGeom g)
+__global__ void __launch_bounds__(kRingThreads, 1) bn_ring_kernel(const FusedArgs a, const RingGeom g)
 {
   extern __shared__ __align__(128) unsigned char sm[];
   RingCtl *ctl = reinterpret_cast<RingCtl *>(sm);
@@ -631,6 +777,7 @@ __global__ void __launch_bounds__(kRingThreads, 2) bn_ring_kernel(const FusedArg
     for (uint32_t i = 0; i < kResQ; ++i) { mbar_init(&ctl->res_full[i], kCWarps); mbar_init(&ctl->res_empty[i], 1); }
     for (uint32_t i = 0; i < kCoefQ; ++i) { mbar_init(&ctl->coef_full[i], 1); mbar_init(&ctl->coef_empty[i], kCWarps); }
     ctl->abort = 0; ctl->last_block = 0;
+    ctl->parity = *ws_u32(a, 8) & 1u;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
@@ -749,31 +896,46 @@ __global__ void __launch_bounds__(kRingThreads, 2) bn_ring_kernel(const FusedArg
       const uint32_t jd = nres + lane;
       const bool d_ok = lane < kResQ && jd < n_red && mbar_test(&ctl->res_full[jd % kResQ], (jd / kResQ) & 1u);
       const uint32_t d_mask = __ballot_sync(0xffffffffu, d_ok);
-      const uint32_t nd = __ffs(~d_mask) - 1;                         // in order: leading run of ones
+      uint32_t nd = __ffs(~d_mask) - 1;                               // in order: leading run of ones
+      if (REGIME == 0 && nd > kPerTurn) nd = kPerTurn;
       RING_PROF(0)
       if (nd) {
         if constexpr (REGIME == 0) {
           // entry e is served by lanes 8e .. 8e+7: one warp partial each, merged in a fixed order
-          const uint32_t e = lane >> 3, w = lane & 7u;
+          const uint32_t e = lane / kCWarps, w = lane % kCWarps;
           float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
           if (e < nd) v = res_box(sm, g, (nres + e) % kResQ)[w];
           if constexpr (DIR == 0) {
             Moments m{v.x, v.y, v.z};
 #pragma unroll
-            for (int o = 4; o > 0; o >>= 1) {
+            for (int o = (int)kCWarps / 2; o > 0; o >>= 1) {
               Moments c;
-              c.n = __shfl_down_sync(0xffffffffu, m.n, o, 8);
-              c.mean = __shfl_down_sync(0xffffffffu, m.mean, o, 8);
-              c.m2 = __shfl_down_sync(0xffffffffu, m.m2, o, 8);
+              c.n = __shfl_down_sync(0xffffffffu, m.n, o, kCWarps);
+              c.mean = __shfl_down_sync(0xffffffffu, m.mean, o, kCWarps);
+              c.m2 = __shfl_down_sync(0xffffffffu, m.m2, o, kCWarps);
               m = merge(m, c);
             }
             v = make_float4(m.n, m.mean, m.m2, 0.f);
           } else {
 #pragma unroll
-            for (int o = 4; o > 0; o >>= 1) {
-              v.x += __shfl_down_sync(0xffffffffu, v.x, o, 8);
-              v.y += __shfl_down_sync(0xffffffffu, v.y, o, 8);
+            for (int o = (int)kCWarps / 2; o > 0; o >>= 1) {
+              v.x += __shfl_down_sync(0xffffffffu, v.x, o, kCWarps);
+              v.y += __shfl_down_sync(0xffffffffu, v.y, o, kCWarps);
             }
+          }
+          if (a.mode == MODE_FUSED) {
+            // one tagged 8-byte word per tile; nothing else to do for a delivery
+            if (e < nd && w == 0) {
+              const size_t t = (size_t)(sc.b + (nres + e) * sc.G);
+              const float lo = DIR == 0 ? v.y : v.x, hi = DIR == 0 ? v.z : v.y;
+              st_relaxed_gpu_u64(tag_buf(a, ctl->parity) + t, pack_rec(lo, __uint_as_float(__float_as_uint(hi) | 1u)));
+              tag_buf(a, ctl->parity ^ 1u)[t] = 0ull;
+            }
+            __syncwarp();
+            if (lane < nd) mbar_arrive(&ctl->res_empty[(nres + lane) % kResQ]);
+            nres += nd;
+            RING_PROF(1)
+            continue;
           }
           if (e < nd && w == 0) __stcg(ws_f4(a, P.off_part) + (size_t)(sc.b + (nres + e) * sc.G), v);
         } else {
@@ -829,6 +991,28 @@ __global__ void __launch_bounds__(kRingThreads, 2) bn_ring_kernel(const FusedArg
     const unsigned long long *rec = reinterpret_cast<const unsigned long long *>(a.ws + P.off_rec);
     uint32_t ncoef = 0;
     long long t_idle = clock64();
+    if (REGIME == 0 && a.mode == MODE_FUSED) {
+      // regime R, fused: merge each unit's partials here (see pull_merge_unit); consecutive visits of
+      // the same unit reuse the result
+      uint32_t have = 0xffffffffu;
+      float4 c0 = make_float4(0.f, 0.f, 0.f, 0.f), c1 = c0;
+      while (ncoef < n_app) {
+        if (!warp_wait(&ctl->coef_empty[ncoef % kCoefQ], ((ncoef / kCoefQ) & 1u) ^ 1u, ctl, status, ANODE_ST_WAIT_STATS)) break;
+        const uint32_t t = sc.b + ncoef * sc.G, u = t / P.tiles_per_unit;
+        if (u != have) {
+          // the block that owns the unit's first tile also writes the per-channel outputs
+          if (!pull_merge_unit<DIR>(a, ctl, status, u, t == u * P.tiles_per_unit, c0, c1)) break;
+          have = u;
+        }
+        if (lane == 0) {
+          float4 *box = coef_box(sm, g, P.cb, ncoef % kCoefQ);
+          box[0] = c0; box[1] = c1;
+          mbar_arrive(&ctl->coef_full[ncoef % kCoefQ]);
+        }
+        ++ncoef;
+      }
+      ncoef = n_app;      // skip the generic loop below
+    }
     while (ncoef < n_app) {
       if (!warp_wait(&ctl->coef_empty[ncoef % kCoefQ], ((ncoef / kCoefQ) & 1u) ^ 1u, ctl, status, ANODE_ST_WAIT_STATS)) break;
       const uint32_t ja = ncoef + lane;
@@ -922,8 +1106,12 @@ __global__ void __launch_bounds__(kRingThreads, 2) bn_ring_kernel(const FusedArg
     }
     __syncthreads();
     if (ctl->last_block) {
-      unsigned long long *rec = reinterpret_cast<unsigned long long *>(a.ws + P.off_rec);
-      for (uint32_t c = tid; c < P.C; c += kRingThreads) rec[c] = 0ull;
+      if constexpr (REGIME == 0) {
+        if (tid == 0) *ws_u32(a, 8) = ctl->parity ^ 1u;       // the next launch uses the other partial buffer
+      } else {
+        unsigned long long *rec = reinterpret_cast<unsigned long long *>(a.ws + P.off_rec);
+        for (uint32_t c = tid; c < P.C; c += kRingThreads) rec[c] = 0ull;
+      }
       if (tid == 0) *exit_ctr = 0;
     }
   }

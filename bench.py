@@ -53,7 +53,7 @@ def hbm_peak():
 
 def local_shape(w, rank, world):
     shape = list(w["shape"])
-    assert shape[w["axis"]] % BLOCKS == 0 and BLOCKS % world == 0
+    assert shape[w["axis"]] % BLOCKS == 0 and BLOCKS % world == 0, "sharded extent must be a multiple of %d" % BLOCKS
     shape[w["axis"]] //= world
     return tuple(shape)
 
@@ -99,7 +99,7 @@ class ClockSampler:
     def start(self):
         try:
             self.p = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q,
-                                       "--format=csv,noheader,nounits", "-lms", "100"],
+                                       "--format=csv,noheader,nounits", "-lms", "20"],
                                       stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except Exception:
             self.p = None
@@ -129,8 +129,10 @@ class ClockSampler:
                 "samples": len(sm), "reasons": sorted(reasons)}
 
 
-def cpu_baseline(w, seconds_hint=15.0):
-    """Times the CPU restatement of the reference's kernel chain on a channel subset."""
+def cpu_baseline(w, steps=3, warmup=0, seconds_hint=20.0):
+    """Times the CPU restatement of the reference's kernel chain on a channel subset, with every
+    host core (torchrun pins OMP_NUM_THREADS to 1; undo that before the OpenMP runtime loads)."""
+    os.environ["OMP_NUM_THREADS"] = str(os.cpu_count() or 1)
     import numpy as np
     from oracle import bn_oracle as o
     shape = list(w["shape"])
@@ -149,17 +151,18 @@ def cpu_baseline(w, seconds_hint=15.0):
     rm, rv = np.zeros(c_sub, np.float32), np.ones(c_sub, np.float32)
     times = []
     t_all = time.perf_counter()
-    for _ in range(3):
+    for i in range(warmup + steps):
         t0 = time.perf_counter()
         o.bn_relu_fwd_bwd_f32(x, dy, 1e-5, 0.1, rm, rv, g, b, block_sz=0)
-        times.append(time.perf_counter() - t0)
-        if time.perf_counter() - t_all > seconds_hint:
+        if i >= warmup:
+            times.append(time.perf_counter() - t0)
+        if time.perf_counter() - t_all > seconds_hint and times:
             break
-    best = min(times)
-    return {"value": x.size / best, "unit": "elements/s", "cores": o.num_threads(), "kind": "port",
-            "sample": "%d of %d channels of %s, %d elements, best of %d runs, f32, 11 passes as the "
+    mean = sum(times) / len(times)
+    return {"value": x.size / mean, "unit": "elements/s", "cores": o.num_threads(), "kind": "port",
+            "sample": "%d of %d channels of %s, %d elements per step, mean of %d steps, f32, the 11 passes of the "
                       "reference's kernel chain" % (c_sub, w["shape"][1], "x".join(map(str, w["shape"])), x.size, len(times)),
-            "seconds": best}, times
+            "seconds": mean}, times
 
 
 def run_reference(args, rank):
@@ -169,13 +172,10 @@ def run_reference(args, rank):
     if rank != 0:
         return
     w = WORKLOADS[args.workload]
-    base, times = cpu_baseline(w, seconds_hint=60.0)
-    # honour --steps/--warmup on the bounded sample
-    import numpy as np
-    from oracle import bn_oracle as o
+    base, times = cpu_baseline(w, steps=args.steps, warmup=args.warmup, seconds_hint=120.0)
     line = {
         "impl": "reference", "metric": "bn_relu_fwd_bwd_elements_per_s", "value": base["value"], "unit": "elements/s",
-        "n_gpus": args.gpus, "steps": len(times), "warmup": 0, "ms_per_step": 1e3 * base["seconds"],
+        "n_gpus": args.gpus, "steps": len(times), "warmup": args.warmup, "ms_per_step": 1e3 * base["seconds"],
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": args.workload + " (CPU: bounded channel subset)", "global_shape": list(w["shape"])},
         "cpu_baseline": base,
@@ -303,13 +303,18 @@ def bench_e2e(ops, layer, x, dy, y, dx, dist, device, steps):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=30)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=DEFAULT, choices=sorted(WORKLOADS))
+    ap.add_argument("--shape", default=None, help="custom global shape N,C,spatial... (N(0,1) data, sharded on axis 0); "
+                    "used for small profiler captures")
     ap.add_argument("--no-extras", action="store_true", help="skip cpu_baseline, e2e and other_workloads")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
+    if args.shape:
+        WORKLOADS["custom"] = dict(shape=tuple(int(v) for v in args.shape.split(",")), dist="normal", loc=0.0, scale=1.0, axis=0)
+        args.workload = "custom"
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -342,6 +347,8 @@ def main():
                 "peak_kind": peak_kind, "traffic": None}
 
     w = WORKLOADS[args.workload]
+    kernel_name = "bn_ring_kernel<%s> (fused reduce+apply)" if world == 1 else \
+        "reduce kernel + all-gather + merge kernel + apply kernel (%s)"
     line = {
         "metric": "bn_relu_fwd_bwd_elements_per_s", "value": main_res["value"], "unit": "elements/s",
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": main_res["ms_per_step"],
@@ -352,8 +359,8 @@ def main():
                    "parallelism": "syncbn_dp%d" % world},
         "per_gpu_value": main_res["value"] / world,
         "fwd_ms": main_res["fwd_ms"], "bwd_ms": main_res["bwd_ms"],
-        "roofline": dict(roof(BYTES_BWD, main_res["bwd_ms"]), kernel="bn_pipeline_kernel<bwd>"),
-        "roofline_fwd": dict(roof(BYTES_FWD, main_res["fwd_ms"]), kernel="bn_pipeline_kernel<fwd>"),
+        "roofline": dict(roof(BYTES_BWD, main_res["bwd_ms"]), kernel=kernel_name % "bwd"),
+        "roofline_fwd": dict(roof(BYTES_FWD, main_res["fwd_ms"]), kernel=kernel_name % "fwd"),
         "roofline_step": roof(BYTES_FWD + BYTES_BWD, main_res["ms_per_step"]),
         "clocks": main_res["clocks"],
         "gpu_launches": main_res["launches_per_step"] * args.steps,
@@ -362,7 +369,7 @@ def main():
         line["e2e"] = main_res["e2e"]
     try:
         with open(os.path.join(ROOT, "profiles", "traffic.json")) as f:
-            tr = json.load(f).get(args.workload if world == 1 else "", {})
+            tr = json.load(f).get(args.workload if world == 1 else "%s@%d" % (args.workload, world), {})
         for key, rk in (("bwd", "roofline"), ("fwd", "roofline_fwd")):
             if key in tr:
                 line[rk]["traffic"] = tr[key]["bytes_per_element"] * main_res["elements_local"]
