@@ -18,10 +18,11 @@ const Tunables &tunables()
 {
   static const Tunables t = {
       env_u32("ANODE_B200_TILE_FLOATS", 32768),
-      env_u32("ANODE_B200_SLACK_STEPS", 3),
+      env_u32("ANODE_B200_SLACK_STEPS", 2),
       env_u32("ANODE_B200_BLOCKS_PER_SM", 4),
       env_u32("ANODE_B200_RING", 1),
       env_u32("ANODE_B200_RING_SLOTS", 3),
+      env_u32("ANODE_B200_RING_SLOTS_BWD", 4),
       env_u32("ANODE_B200_RING_FLOATS_FWD", 16384),
       env_u32("ANODE_B200_RING_FLOATS_BWD", 8192),
       env_u32("ANODE_B200_RING_BLOCKS_PER_SM", 1),
@@ -78,7 +79,8 @@ bool ring_plan_for(uint32_t dim0, uint32_t C, uint32_t N, bool aligned, int dir,
   uint32_t slot_floats = dir == 0 ? t.ring_floats_fwd : t.ring_floats_bwd;
   slot_floats = (slot_floats / 4) * 4;
   if (slot_floats < kSegMaxFloats) slot_floats = kSegMaxFloats;   // a regime-S segment must fit
-  uint32_t slots = t.ring_slots < 2 ? 2 : (t.ring_slots > kMaxSlots ? kMaxSlots : t.ring_slots);
+  uint32_t slots = dir == 0 ? t.ring_slots : t.ring_slots_bwd;
+  slots = slots < 2 ? 2 : (slots > kMaxSlots ? kMaxSlots : slots);
   uint32_t bps = t.ring_blocks_per_sm ? t.ring_blocks_per_sm : 1;
   p = make_plan(dim0, C, N, true, sm_count() * bps, slot_floats, t.slack_steps);
   // regime S (short rows) stays on the plain kernel: its per-unit merge is too slow in one warp
@@ -86,6 +88,7 @@ bool ring_plan_for(uint32_t dim0, uint32_t C, uint32_t N, bool aligned, int dir,
   // a tile must fit one slot: rows * len <= slot_floats
   const uint64_t tile_max = (uint64_t)p.rows_per_tile * p.piece_len;
   if (tile_max > slot_floats) return false;
+  slot_floats = (uint32_t)((tile_max + 31) / 32 * 32);     // slots no larger than the largest tile
   g = ring_geom(p, dir, slots, slot_floats);
   const uint32_t budget = 227u * 1024u;
   while (g.smem_bytes > budget && slots > 2) { --slots; g = ring_geom(p, dir, slots, slot_floats); }

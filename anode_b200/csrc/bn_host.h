@@ -19,7 +19,8 @@ struct Tunables {
   uint32_t slack_steps;     // extra lookahead steps beyond the minimum
   uint32_t blocks_per_sm;   // persistent blocks planned per SM
   uint32_t ring;            // 1: use the warp-specialised kernel where it applies
-  uint32_t ring_slots;      // shared-memory slots per block
+  uint32_t ring_slots;      // shared-memory slots per block (forward)
+  uint32_t ring_slots_bwd;  // shared-memory slots per block (backward; a slot holds x and dy)
   uint32_t ring_floats_fwd; // floats per slot (forward: x)
   uint32_t ring_floats_bwd; // floats per tensor per slot (backward: x and dy)
   uint32_t ring_blocks_per_sm;

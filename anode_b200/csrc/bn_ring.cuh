@@ -249,9 +249,17 @@ __device__ __forceinline__ void warp_reduce_R(const FusedArgs &a, const RingGeom
   const uint32_t cnt = tid < nvec ? (nvec - tid + kConsumers - 1) / kConsumers : 0;   // this thread's vectors
   uint32_t ax = smem_u32(slot_x(sm, g, slot)) + tid * 16;
   if constexpr (DIR == 0) {
-    // shifted sums: K is this thread's first element (see bn_fused.cuh); two accumulator pairs
-    float K = 0.f;
-    if (cnt) K = lds128(ax).v[0];
+    // shifted sums (see bn_fused.cuh), two accumulator pairs
+#ifdef ANODE_RING_PROFILE
+    long long tq0 = clock64();
+#endif
+    // K: the first element of the warp's share (lane 0 has the lowest vector index, so it has a
+    // vector whenever any lane has one).  One shift per warp makes s and q plain sums over lanes.
+    float K = cnt ? lds128(ax).v[0] : 0.f;
+    K = __shfl_sync(0xffffffffu, K, 0);
+#ifdef ANODE_RING_PROFILE
+    long long tq1 = clock64();
+#endif
     float s0 = 0.f, q0 = 0.f, s1 = 0.f, q1 = 0.f;
     uint32_t i = 0;
     for (; i + 4 <= cnt; i += 4, ax += 4 * kVecStride) {
@@ -263,23 +271,46 @@ __device__ __forceinline__ void warp_reduce_R(const FusedArgs &a, const RingGeom
         s0 += d2; q0 = fmaf(d2, d2, q0); s1 += d3; q1 = fmaf(d3, d3, q1);
       }
     }
-    for (; i < cnt; ++i, ax += kVecStride) {
+    for (; i + 2 <= cnt; i += 2, ax += 2 * kVecStride) {
+      const Pack<4> v0 = lds128(ax), v1 = lds128(ax + kVecStride);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float d0 = v0.v[e] - K, d1 = v1.v[e] - K;
+        s0 += d0; q0 = fmaf(d0, d0, q0); s1 += d1; q1 = fmaf(d1, d1, q1);
+      }
+    }
+    if (i < cnt) {
       const Pack<4> v0 = lds128(ax);
 #pragma unroll
       for (int e = 0; e < 4; ++e) { const float d0 = v0.v[e] - K; s0 += d0; q0 = fmaf(d0, d0, q0); }
     }
+#ifdef ANODE_RING_PROFILE
+    long long tq2 = clock64();
+#endif
     __syncwarp();
     if (lane == 0) mbar_arrive(&ctl->empty[slot]);
-    const float s = s0 + s1, q = q0 + q1;
-    Moments m{0.f, 0.f, 0.f};
-    if (cnt) {
-      m.n = (float)(cnt * 4);
-      const float inv = __fdividef(1.0f, m.n);
-      m.mean = fmaf(s, inv, K);
-      m.m2 = fmaxf(q - s * s * inv, 0.f);
+#ifdef ANODE_RING_PROFILE
+    long long tq3 = clock64();
+#endif
+    const float s = warp_sum(s0 + s1), q = warp_sum(q0 + q1);
+    const uint32_t nw = __reduce_add_sync(0xffffffffu, cnt * 4);
+    if (lane == 0) {
+      Moments m{0.f, 0.f, 0.f};
+      if (nw) {
+        m.n = (float)nw;
+        const float inv = __fdividef(1.0f, m.n);
+        m.mean = fmaf(s, inv, K);
+        m.m2 = fmaxf(q - s * s * inv, 0.f);
+      }
+      res[warp] = make_float4(m.n, m.mean, m.m2, 0.f);
     }
-    m = warp_merge(m);
-    if (lane == 0) res[warp] = make_float4(m.n, m.mean, m.m2, 0.f);
+#ifdef ANODE_RING_PROFILE
+    if (blockIdx.x == 0 && tid == 0) {
+      long long tq4 = clock64();
+      unsigned long long *dbg = reinterpret_cast<unsigned long long *>(a.ws + a.ws_capacity - 256 * 1024);
+      dbg[0] += tq1 - tq0; dbg[1] += tq2 - tq1; dbg[2] += tq3 - tq2; dbg[3] += tq4 - tq3; dbg[4] += 1; dbg[5] += cnt;
+    }
+#endif
   } else {
     uint32_t ad = ax + g.slot_floats * 4;
     const float4 cf = slot_side<1>(sm, g, slot)[0];
