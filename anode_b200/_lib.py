@@ -64,6 +64,8 @@ SIGNATURES = {
     "anode_gpu_sync_batch_norm_relu_bwd_3d1_packed_f32":
         (c_int, _D + [ctypes.c_uint64, c_int, c_int] + [vp] * 9 + [vp, vp, size_t] + _T),
     "anode_gpu_batch_norm_fused_plan": (c_int, _D + [c_int, u32, u32, u32, ctypes.POINTER(u32), u32]),
+    "anode_gpu_batch_norm_fused_plan_walk":
+        (c_int, _D + [c_int, u32, u32, u32, u32, u32, ctypes.POINTER(ctypes.c_uint64)]),
     "anode_gpu_batch_norm_fused_plan_tile":
         (c_int, _D + [c_int, u32, u32, u32, ctypes.POINTER(ctypes.c_uint64)]),
 }

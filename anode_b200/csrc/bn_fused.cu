@@ -1,7 +1,17 @@
 // Host side of the fused batch-norm (+ReLU) entry points: argument checks, the tile plan,
 // and the cooperative launch of the persistent kernels of bn_fused.cuh.
 #include "bn_host.h"
+// the warp-specialised kernel, instantiated with 8 and with 16 consumer warps
+#define ANODE_RING_NS ring8
+#define ANODE_RING_CONSUMERS 256
 #include "bn_ring.cuh"
+#undef ANODE_RING_NS
+#undef ANODE_RING_CONSUMERS
+#define ANODE_RING_NS ring16
+#define ANODE_RING_CONSUMERS 512
+#include "bn_ring.cuh"
+#undef ANODE_RING_NS
+#undef ANODE_RING_CONSUMERS
 
 namespace anode_b200 {
 
@@ -26,6 +36,8 @@ const Tunables &tunables()
       env_u32("ANODE_B200_RING_FLOATS_FWD", 16384),
       env_u32("ANODE_B200_RING_FLOATS_BWD", 8192),
       env_u32("ANODE_B200_RING_BLOCKS_PER_SM", 1),
+      env_u32("ANODE_B200_RING_WARPS_FWD", 8),
+      env_u32("ANODE_B200_RING_WARPS_BWD", 16),
   };
   return t;
 }
@@ -55,12 +67,20 @@ Plan plan_for(uint32_t dim0, uint32_t C, uint32_t N, bool aligned16)
 }
 
 // Shared-memory layout of the warp-specialised kernel for plan `p` (see bn_ring.cuh).
+// consumer warps of direction `dir`: 8 or 16 (the two instantiations of bn_ring.cuh)
+static uint32_t ring_warps(int dir)
+{
+  const Tunables &t = tunables();
+  return (dir == 0 ? t.ring_warps_fwd : t.ring_warps_bwd) >= 16 ? 16u : 8u;
+}
+
 static RingGeom ring_geom(const Plan &p, int dir, uint32_t slots, uint32_t slot_floats)
 {
   RingGeom g{};
   g.slots = slots; g.slot_floats = slot_floats;
-  uint32_t off = (uint32_t)align_up_u64(sizeof(RingCtl), 128);
-  g.res_stride = p.cb > kConsumers / 32 ? p.cb : kConsumers / 32;   // regime R: one partial per consumer warp
+  uint32_t off = kRingCtlBytes;
+  const uint32_t cwarps = ring_warps(dir);
+  g.res_stride = p.cb > cwarps ? p.cb : cwarps;   // regime R: one partial per consumer warp
   g.off_res = off;  off += (uint32_t)align_up_u64((uint64_t)kResQ * g.res_stride * 16, 128);
   g.off_coef = off; off += (uint32_t)align_up_u64((uint64_t)kCoefQ * p.cb * 32, 128);
   g.off_seg = off;  if (p.regime == 1) off += 2 * kSegMaxFloats * 4;
@@ -98,15 +118,22 @@ bool ring_plan_for(uint32_t dim0, uint32_t C, uint32_t N, bool aligned, int dir,
 
 typedef void (*RingKernel)(const FusedArgs, const RingGeom);
 
-static RingKernel pick_ring_kernel(const Plan &p, int dir)
+static RingKernel pick_ring_kernel(const Plan &p, int dir, uint32_t &threads)
 {
-  if (p.regime == 1) return dir == 0 ? bn_ring_kernel<0, 1> : bn_ring_kernel<1, 1>;
-  return dir == 0 ? bn_ring_kernel<0, 0> : bn_ring_kernel<1, 0>;
+  // only regime R reaches this point (ring_plan_for)
+  (void)p;
+  if (ring_warps(dir) == 16) {
+    threads = ring16::kRingThreads;
+    return dir == 0 ? ring16::bn_ring_kernel<0, 0> : ring16::bn_ring_kernel<1, 0>;
+  }
+  threads = ring8::kRingThreads;
+  return dir == 0 ? ring8::bn_ring_kernel<0, 0> : ring8::bn_ring_kernel<1, 0>;
 }
 
 int launch_ring(FusedArgs &a, const RingGeom &g, int dir, cudaStream_t stream)
 {
-  RingKernel k = pick_ring_kernel(a.plan, dir);
+  uint32_t threads = 0;
+  RingKernel k = pick_ring_kernel(a.plan, dir, threads);
   static std::mutex mu;
   static std::map<std::pair<const void *, uint32_t>, int> occ;     // (kernel, smem) -> blocks per SM
   int per_sm = 0;
@@ -116,7 +143,7 @@ int launch_ring(FusedArgs &a, const RingGeom &g, int dir, cudaStream_t stream)
     auto it = occ.find(key);
     if (it == occ.end()) {
       if (cudaFuncSetAttribute((const void *)k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(227 * 1024)) != cudaSuccess ||
-          cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, k, (int)kRingThreads, g.smem_bytes) != cudaSuccess) {
+          cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, k, (int)threads, g.smem_bytes) != cudaSuccess) {
         (void)cudaGetLastError();
         per_sm = 0;
       }
@@ -135,9 +162,9 @@ int launch_ring(FusedArgs &a, const RingGeom &g, int dir, cudaStream_t stream)
   void *params[] = {(void *)&a, (void *)&g};
   cudaError_t e;
   if (a.mode == MODE_FUSED)
-    e = cudaLaunchCooperativeKernel((const void *)k, dim3(a.plan.grid), dim3(kRingThreads), params, g.smem_bytes, stream);
+    e = cudaLaunchCooperativeKernel((const void *)k, dim3(a.plan.grid), dim3(threads), params, g.smem_bytes, stream);
   else
-    e = cudaLaunchKernel((const void *)k, dim3(a.plan.grid), dim3(kRingThreads), params, g.smem_bytes, stream);
+    e = cudaLaunchKernel((const void *)k, dim3(a.plan.grid), dim3(threads), params, g.smem_bytes, stream);
   if (e != cudaSuccess) { (void)cudaGetLastError(); return ANODE_E_LAUNCH; }
   return ANODE_OK;
 }
@@ -382,5 +409,27 @@ extern "C" int anode_gpu_batch_norm_fused_plan_tile(uint32_t dim0, uint32_t dim1
   const TileRange r = tile_range(p, tile);
   out[0] = r.unit; out[1] = r.c0; out[2] = r.cw; out[3] = r.n0; out[4] = r.rows; out[5] = r.col0;
   out[6] = r.len; out[7] = r.base;
+  return ANODE_OK;
+}
+
+// Walks `count` tiles first, first+stride, ... with the division-free iterator the kernels use.
+// out: 8 values per tile as in anode_gpu_batch_norm_fused_plan_tile.
+extern "C" int anode_gpu_batch_norm_fused_plan_walk(uint32_t dim0, uint32_t dim1, uint32_t dim2, int aligned,
+                                                    uint32_t resident_blocks, uint32_t tile_floats,
+                                                    uint32_t first, uint32_t stride, uint32_t count, uint64_t *out)
+{
+  if (!out || check_dims(dim0, dim1, dim2) || stride == 0) return ANODE_E_DIMS;
+  const Tunables &t = tunables();
+  const Plan p = make_plan(dim0, dim1, dim2, aligned != 0,
+                           resident_blocks ? resident_blocks : sm_count() * t.blocks_per_sm,
+                           tile_floats ? tile_floats : t.tile_floats, t.slack_steps);
+  TileIter it; it.init(p, first, stride);
+  for (uint32_t i = 0; i < count; ++i) {
+    if (it.tile() >= p.total_tiles) return ANODE_E_DIMS;
+    const TileRange r = it.range(p);
+    uint64_t *o = out + 8 * (size_t)i;
+    o[0] = r.unit; o[1] = r.c0; o[2] = r.cw; o[3] = r.n0; o[4] = r.rows; o[5] = r.col0; o[6] = r.len; o[7] = r.base;
+    it.advance(p);
+  }
   return ANODE_OK;
 }

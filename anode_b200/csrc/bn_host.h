@@ -24,6 +24,8 @@ struct Tunables {
   uint32_t ring_floats_fwd; // floats per slot (forward: x)
   uint32_t ring_floats_bwd; // floats per tensor per slot (backward: x and dy)
   uint32_t ring_blocks_per_sm;
+  uint32_t ring_warps_fwd;  // consumer warps of the forward kernel (8 or 16)
+  uint32_t ring_warps_bwd;  // consumer warps of the backward kernel (8 or 16)
 };
 const Tunables &tunables();
 

@@ -92,6 +92,48 @@ ANODE_HD TileRange tile_range(const Plan &p, uint32_t t)
   return r;
 }
 
+// Walks the tiles b, b+G, b+2G, ... of one thread block without a division per tile (a block
+// visits hundreds of tiles and every thread needs each tile's range).  range() equals
+// tile_range(p, tile()).
+struct TileIter {
+  uint32_t t, unit, k, G;
+  ANODE_HD void init(const Plan &p, uint32_t first, uint32_t stride)
+  {
+    t = first; G = stride;
+    unit = t / p.tiles_per_unit;
+    k = t - unit * p.tiles_per_unit;
+  }
+  ANODE_HD uint32_t tile() const { return t; }
+  ANODE_HD void advance(const Plan &p)
+  {
+    t += G; k += G;
+    if (k >= p.tiles_per_unit) {
+      if (k - p.tiles_per_unit < p.tiles_per_unit) { k -= p.tiles_per_unit; ++unit; }
+      else { const uint32_t q = k / p.tiles_per_unit; unit += q; k -= q * p.tiles_per_unit; }
+    }
+  }
+  ANODE_HD TileRange range(const Plan &p) const
+  {
+    TileRange r;
+    r.unit = unit;
+    uint32_t sb = k, piece = 0;
+    if (p.pieces != 1) { sb = k / p.pieces; piece = k - sb * p.pieces; }
+    r.c0 = unit * p.cb;
+    r.cw = (p.C - r.c0 < p.cb) ? (p.C - r.c0) : p.cb;
+    r.n0 = sb * p.rows_per_tile;
+    r.rows = (p.N - r.n0 < p.rows_per_tile) ? (p.N - r.n0) : p.rows_per_tile;
+    if (p.regime == 0) {
+      r.col0 = piece * p.piece_len;
+      r.len = (p.dim0 - r.col0 < p.piece_len) ? (p.dim0 - r.col0) : p.piece_len;
+    } else {
+      r.col0 = 0;
+      r.len = r.cw * p.dim0;
+    }
+    r.base = ((uint64_t)r.n0 * p.C + r.c0) * p.dim0 + r.col0;
+    return r;
+  }
+};
+
 inline uint32_t ceil_div_u32(uint32_t a, uint32_t b) { return (a + b - 1) / b; }
 inline uint64_t align_up_u64(uint64_t a, uint64_t b) { return (a + b - 1) / b * b; }
 

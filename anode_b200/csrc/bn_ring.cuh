@@ -20,23 +20,35 @@
 //
 // Every wait is bounded: a wait that runs out sets a status bit, raises the block's abort flag
 // and all three roles drain and leave.
-#pragma once
+// This header has no include guard on purpose: it is included once per consumer-warp count, with
+// ANODE_RING_NS naming the namespace of the instantiation and ANODE_RING_CONSUMERS the number of
+// consumer threads (the forward pass runs best with 8 consumer warps, the backward pass with 16).
 #include "bn_fused.cuh"
 
-namespace anode_b200 {
-
-#ifndef ANODE_RING_CONSUMERS
-#define ANODE_RING_CONSUMERS 512
+#if !defined(ANODE_RING_NS) || !defined(ANODE_RING_CONSUMERS)
+#error "define ANODE_RING_NS and ANODE_RING_CONSUMERS before including bn_ring.cuh"
 #endif
+#ifndef ANODE_RING_STORE
+#define ANODE_RING_STORE 1      // 0: store with an L2 evict-first hint, 1: st.global.cs, 2: plain store
+#endif
+#ifndef ANODE_RING_BACKOFF_NS
+#define ANODE_RING_BACKOFF_NS 100
+#endif
+#ifndef ANODE_RING_COPY_BYTES
+#define ANODE_RING_COPY_BYTES 32768
+#endif
+
+namespace anode_b200 {
+namespace ANODE_RING_NS {
+
 constexpr uint32_t kConsumers = ANODE_RING_CONSUMERS;   // consumer threads (a power of two, 256..1024)
 constexpr uint32_t kRingThreads = kConsumers + 96;   // + producer, delivery and coefficient warps
-constexpr uint32_t kResQ = 4;                        // partial mailbox depth
-constexpr uint32_t kCoefQ = 4;                       // coefficient mailbox depth
-constexpr uint32_t kMaxSlots = 8;
+constexpr uint32_t kCopyBytes = ANODE_RING_COPY_BYTES;   // size of one bulk copy (a multiple of 16)
 constexpr long long kWaitCycles = 3000000000ll;      // about 1.5 s at 2 GHz
 
 // Optional per-block cycle accounting (build with -DANODE_RING_PROFILE): 16 counters per block are
 // written behind the regular workspace contents.
+#ifndef RING_PROF_DECL
 #ifdef ANODE_RING_PROFILE
 #define RING_PROF_DECL long long pf_t = clock64(); long long pf[8] = {0, 0, 0, 0, 0, 0, 0, 0};
 #define RING_PROF(i) { const long long pf_n = clock64(); pf[i] += pf_n - pf_t; pf_t = pf_n; }
@@ -50,6 +62,7 @@ __device__ __forceinline__ unsigned long long gtimer() { unsigned long long t; a
 #define RING_PROF_OUT(base) {}
 #define RING_TL(idx, val) {}
 #endif
+#endif   // RING_PROF_DECL
 
 struct RingCtl {
   unsigned long long full[kMaxSlots], empty[kMaxSlots];
@@ -60,6 +73,7 @@ struct RingCtl {
   uint32_t last_block;
   uint32_t parity;       // which of the two tagged-partial buffers this launch uses
 };
+static_assert(sizeof(RingCtl) <= kRingCtlBytes, "RingCtl outgrew the room reserved for it");
 
 // ---- mbarrier / bulk-copy primitives --------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -101,11 +115,15 @@ __device__ __forceinline__ bool mbar_wait(unsigned long long *bar, uint32_t pari
   uint32_t it = 0;
   for (;;) {
     if (mbar_try(bar, parity)) return true;
-    if (ctl->abort) return false;
-    if ((++it & 63u) == 0u && clock64() - t0 > kWaitCycles) {
-      atomicOr(status, bit);
-      ctl->abort = 1;
-      return false;
+    // back off: a spinning waiter takes issue slots from the warps that do the work
+    __nanosleep(ANODE_RING_BACKOFF_NS);
+    if ((++it & 15u) == 0u) {
+      if (ctl->abort) return false;
+      if (clock64() - t0 > kWaitCycles) {
+        atomicOr(status, bit);
+        ctl->abort = 1;
+        return false;
+      }
     }
   }
 }
@@ -184,6 +202,7 @@ struct Sched {
   uint32_t my_tiles, look, b, G;
   bool do_reduce, do_apply;
   uint32_t s, phase;     // phase 0: reduce of step s pending; 1: apply of step s pending
+  TileIter it_reduce, it_apply;     // the reduce visits and the apply visits both walk b, b+G, ...
   __device__ __forceinline__ void init(const FusedArgs &a)
   {
     b = blockIdx.x; G = gridDim.x;
@@ -191,6 +210,22 @@ struct Sched {
     look = (a.mode == MODE_FUSED) ? a.plan.lookahead_steps : 0;
     do_reduce = a.mode != MODE_APPLY; do_apply = a.mode != MODE_STATS;
     s = 0; phase = 0;
+    it_reduce.init(a.plan, b, G); it_apply.init(a.plan, b, G);
+  }
+  // Same walk, but hands out the tile's range without any per-tile division.
+  __device__ __forceinline__ bool next_range(const Plan &P, uint32_t &kind, TileRange &tr)
+  {
+    for (;;) {
+      if (s >= my_tiles + look) return false;
+      if (phase == 0) {
+        phase = 1;
+        if (do_reduce && s < my_tiles) { kind = 0; tr = it_reduce.range(P); it_reduce.advance(P); return true; }
+      } else {
+        phase = 0;
+        const uint32_t ss = s++;
+        if (do_apply && ss >= look) { kind = 1; tr = it_apply.range(P); it_apply.advance(P); return true; }
+      }
+    }
   }
   // Advances to the next operation; returns false at the end.  kind: 0 reduce, 1 apply.
   __device__ __forceinline__ bool next(uint32_t &kind, uint32_t &tile)
@@ -209,9 +244,6 @@ struct Sched {
   }
 };
 
-struct RingGeom {
-  uint32_t slots, slot_floats, slot_stride, res_stride, off_res, off_coef, off_seg, off_slots, smem_bytes;
-};
 
 // dynamic shared memory accessors
 __device__ __forceinline__ float *slot_x(unsigned char *sm, const RingGeom &g, uint32_t slot) { return reinterpret_cast<float *>(sm + g.off_slots + (size_t)slot * g.slot_stride); }
@@ -386,7 +418,13 @@ __device__ __forceinline__ void warp_apply_R(const FusedArgs &a, const RingGeom 
         o.v[e] = acc ? o.v[e] + dx : dx;
       }
     }
+#if ANODE_RING_STORE == 1
+    o.store_stream(dst);
+#elif ANODE_RING_STORE == 2
+    *reinterpret_cast<float4 *>(dst) = make_float4(o.v[0], o.v[1], o.v[2], o.v[3]);
+#else
     o.store(dst, drop);
+#endif
   }
   __syncwarp();
   if (lane == 0) { mbar_arrive(&ctl->empty[slot]); mbar_arrive(&ctl->coef_empty[coef_q]); }
@@ -730,15 +768,23 @@ __device__ __forceinline__ bool pull_merge_unit(const FusedArgs &a, RingCtl *ctl
       if (__shfl_sync(0xffffffffu, stop, 0)) return false;
     }
     if constexpr (DIR == 0) {
-      double nk[kPullRegs];
+      // element count of partial k, from the tile geometry (no division when rows are not split)
+      auto count_of = [&](uint32_t k) -> float {
+        if (k >= T) return 0.f;
+        uint32_t sb = k, piece = 0;
+        if (P.pieces != 1) { sb = k / P.pieces; piece = k - sb * P.pieces; }
+        const uint32_t n0 = sb * P.rows_per_tile, col0 = piece * P.piece_len;
+        const uint32_t rows = (P.N - n0 < P.rows_per_tile) ? (P.N - n0) : P.rows_per_tile;
+        const uint32_t len = (P.dim0 - col0 < P.piece_len) ? (P.dim0 - col0) : P.piece_len;
+        return (float)(rows * len);
+      };
+      float nk[kPullRegs];
       double sn = 0.0, sm = 0.0;
 #pragma unroll
       for (int i = 0; i < kPullRegs; ++i) {
-        const uint32_t k = k0 + lane + 32u * i;
-        nk[i] = 0.0;
-        if (k < T) { const TileRange tr = tile_range(P, u * T + k); nk[i] = (double)tr.rows * (double)tr.len; }
+        nk[i] = count_of(k0 + lane + 32u * i);
         const double mk = (double)__uint_as_float((uint32_t)(r[i] & 0xffffffffull));
-        sn += nk[i]; sm = fma(nk[i], mk, sm);
+        sn += (double)nk[i]; sm = fma((double)nk[i], mk, sm);
       }
       sn = warp_sum_all(sn); sm = warp_sum_all(sm);
       const double mean = sm / sn;
@@ -748,7 +794,7 @@ __device__ __forceinline__ bool pull_merge_unit(const FusedArgs &a, RingCtl *ctl
         const double mk = (double)__uint_as_float((uint32_t)(r[i] & 0xffffffffull));
         const double m2 = (double)__uint_as_float((uint32_t)(r[i] >> 32));
         const double d = mk - mean;
-        if (nk[i] > 0.0) sq += m2 + nk[i] * d * d;
+        if (nk[i] > 0.f) sq += m2 + (double)nk[i] * d * d;
       }
       sq = warp_sum_all(sq);
       tot = merge64(tot, Moments64{sn, mean, sq});
@@ -815,15 +861,16 @@ __global__ void __launch_bounds__(kRingThreads, 1) bn_ring_kernel(const FusedArg
   __syncthreads();
 
   Sched sc; sc.init(a);
-  uint32_t kind, tile;
+  uint32_t kind;
 
   if (warp < kConsumers / 32) {
     // ------------------------------------------------------------------ consumers
-    uint32_t k = 0, nres = 0, ncoef = 0;      // ring position, reduce count, apply count
+    uint32_t nres = 0, ncoef = 0;             // reduce count, apply count
+    uint32_t slot = g.slots - 1, par = 1;     // ring position, stepped without divisions
+    TileRange tr;
     RING_PROF_DECL
-    while (sc.next(kind, tile)) {
-      const uint32_t slot = k % g.slots, par = (k / g.slots) & 1u; ++k;
-      const TileRange tr = tile_range(P, tile);
+    while (sc.next_range(P, kind, tr)) {
+      if (++slot == g.slots) { slot = 0; par ^= 1u; }
       if (kind == 0) {
         const uint32_t q = nres % kResQ, qpar = (nres / kResQ) & 1u; ++nres;
         // the partial mailbox entry must have been emptied by the delivery warp (first pass: free)
@@ -869,11 +916,13 @@ __global__ void __launch_bounds__(kRingThreads, 1) bn_ring_kernel(const FusedArg
     const uint64_t keep = policy_keep(), drop = policy_drop();
     const uint64_t rs = (uint64_t)P.C * P.dim0;
     uint32_t k = 0;
+    uint32_t slot = g.slots - 1, par = 1;
     bool ok = true;
+    TileRange tr;
     RING_PROF_DECL
-    while (ok && sc.next(kind, tile)) {
-      const uint32_t slot = k % g.slots, par = (k / g.slots) & 1u; ++k;
-      const TileRange tr = tile_range(P, tile);
+    while (ok && sc.next_range(P, kind, tr)) {
+      ++k;
+      if (++slot == g.slots) { slot = 0; par ^= 1u; }
       uint32_t okw = 1;
       if (lane == 0) okw = mbar_wait(&ctl->empty[slot], par ^ 1u, ctl, status, ANODE_ST_WAIT_STATS) ? 1u : 0u;
       ok = __shfl_sync(0xffffffffu, okw, 0) != 0;     // one lane decides for the warp
@@ -893,11 +942,21 @@ __global__ void __launch_bounds__(kRingThreads, 1) bn_ring_kernel(const FusedArg
       const uint32_t row_bytes = tr.len * 4u;
       if (lane == 0) mbar_arrive_expect_tx(&ctl->full[slot], row_bytes * tr.rows * (DIR == 1 ? 2u : 1u));
       __syncwarp();
+#ifdef ANODE_RING_NO_KEEP
+      const uint64_t pol = drop;
+#else
       const uint64_t pol = (kind == 0 && a.mode == MODE_FUSED) ? keep : drop;
-      for (uint32_t r = lane; r < tr.rows; r += 32) {
-        const size_t goff = (size_t)tr.base + (size_t)r * rs;
-        bulk_g2s(xs + (size_t)r * tr.len, a.x + goff, row_bytes, &ctl->full[slot], pol);
-        if (DIR == 1) bulk_g2s(xs + g.slot_floats + (size_t)r * tr.len, a.dy + goff, row_bytes, &ctl->full[slot], pol);
+#endif
+      // every row is fetched as several bulk copies (one per lane at a time), so that a tile made of
+      // one long row still has many copies in flight
+      const uint32_t per_row = (row_bytes + kCopyBytes - 1) / kCopyBytes, ncopies = per_row * tr.rows;
+      for (uint32_t c = lane; c < ncopies; c += 32) {
+        const uint32_t r = c / per_row, o = (c - r * per_row) * kCopyBytes;
+        const uint32_t nb = row_bytes - o < kCopyBytes ? row_bytes - o : kCopyBytes;
+        const size_t goff = (size_t)tr.base + (size_t)r * rs + o / 4;
+        float *dst = xs + (size_t)r * tr.len + o / 4;
+        bulk_g2s(dst, a.x + goff, nb, &ctl->full[slot], pol);
+        if (DIR == 1) bulk_g2s(dst + g.slot_floats, a.dy + goff, nb, &ctl->full[slot], pol);
       }
       RING_PROF(1)
     }
@@ -1148,4 +1207,5 @@ __global__ void __launch_bounds__(kRingThreads, 1) bn_ring_kernel(const FusedArg
   }
 }
 
+}  // namespace ANODE_RING_NS
 }  // namespace anode_b200

@@ -86,3 +86,22 @@ def test_fast_division_is_exact_in_its_domain():
             n = np.unique(np.concatenate([n[:5000], n[-5000:], rng.choice(n, 5000)]))
         q = (n * np.uint64(mul)) >> np.uint64(32)
         assert (q == n // np.uint64(d)).all(), d
+
+
+@pytest.mark.parametrize("d0,c,n", SHAPES)
+def test_division_free_walk_equals_per_tile_ranges(d0, c, n):
+    """The kernels step from tile to tile with an iterator that avoids divisions; it must give
+    exactly the ranges of the direct formula, for strides below and above tiles_per_unit."""
+    p = plan(d0, c, n, True, resident=64, tile_floats=2048)
+    total = p["total_tiles"]
+    for first, stride in ((0, 1), (3, 7), (1, 64), (0, max(1, p["tiles_per_unit"] * 2 + 1)), (5, 1000)):
+        if first >= total:
+            continue
+        count = (total - first + stride - 1) // stride
+        out = (ctypes.c_uint64 * (8 * count))()
+        rc = _lib.load().anode_gpu_batch_norm_fused_plan_walk(d0, c, n, 1, 64, 2048, first, stride, count, out)
+        assert rc == 0
+        for i in range(0, count, max(1, count // 50)):
+            want = tile(d0, c, n, first + i * stride, True, resident=64, tile_floats=2048)
+            got = dict(zip(["unit", "c0", "cw", "n0", "rows", "col0", "len", "base"], list(out[8 * i:8 * i + 8])))
+            assert got == want, (first, stride, i)
