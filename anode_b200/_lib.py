@@ -58,6 +58,8 @@ SIGNATURES = {
     "anode_gpu_sync_get_unique_id": (c_int, [vp]),
     "anode_gpu_sync_comm_create": (c_int, [vp, c_int, c_int, ctypes.POINTER(vp)]),
     "anode_gpu_sync_comm_destroy": (c_int, [vp]),
+    "anode_gpu_sync_exchange_bytes": (size_t, [u32, c_int]),
+    "anode_gpu_sync_comm_attach_exchange": (c_int, [vp, ctypes.POINTER(vp), u32]),
     "anode_gpu_sync_batch_norm_workspace_bytes": (size_t, _D + [c_int]),
     "anode_gpu_sync_batch_norm_relu_fwd_3d1_packed_f32":
         (c_int, _D + [f32, f32, c_int] + [vp] * 8 + [vp, vp, size_t] + _T),

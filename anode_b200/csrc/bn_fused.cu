@@ -181,6 +181,13 @@ uint64_t control_region_bytes(uint32_t dim0, uint32_t C, uint32_t N, bool aligne
   return n;
 }
 
+// True when the warp-specialised kernel will serve this call (the in-kernel exchange needs it).
+bool ring_applies(const FusedArgs &a, int dir, bool aligned)
+{
+  Plan rp; RingGeom g;
+  return ring_plan_for(a.plan.dim0, a.plan.C, a.plan.N, aligned, dir, rp, g) && rp.ws_bytes <= a.ws_capacity;
+}
+
 // Launches direction `dir` of a prepared call with the best kernel that applies.
 int launch_best(FusedArgs &a, int dir, bool aligned, cudaStream_t stream)
 {

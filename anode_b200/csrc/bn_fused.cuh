@@ -41,6 +41,10 @@ struct FusedArgs {
   uint32_t relu, accumulate, mode;
   uint32_t use_rec;        // publish tagged records (the warp-specialised kernel reads them)
   double count_total;      // elements per channel over all participating GPUs
+  // cross-GPU exchange inside the kernel (world > 1): xchg[r] is rank r's exchange buffer as
+  // mapped into this process (xchg[rank] is local memory); see bn_ring.cuh
+  uint32_t rank, world, epoch, xchg_channels;
+  unsigned long long *xchg[8];
 };
 
 // 1/sqrt(v) as every kernel here computes it (IEEE divide and square root), so that the

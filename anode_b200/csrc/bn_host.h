@@ -44,6 +44,7 @@ int prepare_bwd(FusedArgs &a, uint32_t dim0, uint32_t dim1, uint32_t dim2, int r
 int launch_pipeline(FusedArgs &a, int dir, cudaStream_t stream);
 // picks the warp-specialised kernel where it applies, the plain one otherwise
 int launch_best(FusedArgs &a, int dir, bool aligned, cudaStream_t stream);
+bool ring_applies(const FusedArgs &a, int dir, bool aligned);
 uint64_t control_region_bytes(uint32_t dim0, uint32_t C, uint32_t N, bool aligned);
 
 }  // namespace anode_b200

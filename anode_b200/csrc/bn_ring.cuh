@@ -729,6 +729,16 @@ __device__ __forceinline__ void st_relaxed_gpu_u64(unsigned long long *p, unsign
 {
   asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
 }
+__device__ __forceinline__ unsigned long long ld_relaxed_sys_u64(const unsigned long long *p)
+{
+  unsigned long long v;
+  asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_relaxed_sys_u64(unsigned long long *p, unsigned long long v)
+{
+  asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
 constexpr int kPullRegs = 8;      // partial words per lane per round (256 tiles per round)
 
 // Whole warp.  Returns false when the wait ran out (abort raised).  On success c0 / c1 hold the
@@ -748,7 +758,10 @@ __device__ __forceinline__ bool pull_merge_unit(const FusedArgs &a, RingCtl *ctl
   Moments64 tot{0.0, 0.0, 0.0};
   double s1 = 0.0, s2 = 0.0;
   const long long t0 = clock64();
-  for (uint32_t k0 = 0; k0 < T; k0 += 32u * kPullRegs) {
+  // With several GPUs only the unit's owner block needs the local merge (it ships the result to
+  // every rank); all other blocks go straight to the exchanged records.
+  const bool local = (a.world <= 1) || owner;
+  for (uint32_t k0 = 0; local && k0 < T; k0 += 32u * kPullRegs) {
     unsigned long long r[kPullRegs];
     for (;;) {
       bool all = true;
@@ -809,6 +822,58 @@ __device__ __forceinline__ bool pull_merge_unit(const FusedArgs &a, RingCtl *ctl
       }
     }
   }
+  if constexpr (DIR == 1) { if (local) { s1 = warp_sum_all(s1); s2 = warp_sum_all(s2); } }
+  if (a.world > 1) {
+    // ---- exchange between GPUs.  A record is three 8-byte words (value in the low half, the
+    // call's epoch in the high half): every word validates itself, so plain peer stores suffice
+    // and nothing is ever zeroed; consecutive calls alternate between two buffers.
+    const uint32_t par = a.epoch & 1u;
+    const size_t slot = (((size_t)par * a.world) * a.xchg_channels + u) * 4;      // + src * xchg_channels * 4
+    const size_t src_stride = (size_t)a.xchg_channels * 4;
+    if (owner && lane < a.world) {
+      const float w0 = DIR == 0 ? (float)tot.n : (float)s1;
+      const float w1 = DIR == 0 ? (float)tot.mean : (float)s2;
+      const float w2 = DIR == 0 ? (float)tot.m2 : 0.f;
+      unsigned long long *dst = a.xchg[lane] + slot + a.rank * src_stride;       // this rank's slot in peer `lane`
+      const unsigned long long e = (unsigned long long)a.epoch << 32;
+      st_relaxed_sys_u64(dst + 0, e | __float_as_uint(w0));
+      st_relaxed_sys_u64(dst + 1, e | __float_as_uint(w1));
+      st_relaxed_sys_u64(dst + 2, e | __float_as_uint(w2));
+    }
+    // lane r collects rank r's record from this GPU's own buffer
+    const unsigned long long *mine = a.xchg[a.rank] + slot + (lane < a.world ? lane : 0) * src_stride;
+    unsigned long long v0 = 0, v1 = 0, v2 = 0;
+    for (;;) {
+      bool ok = true;
+      if (lane < a.world) {
+        v0 = ld_relaxed_sys_u64(mine + 0); v1 = ld_relaxed_sys_u64(mine + 1); v2 = ld_relaxed_sys_u64(mine + 2);
+        ok = (uint32_t)(v0 >> 32) == a.epoch && (uint32_t)(v1 >> 32) == a.epoch && (uint32_t)(v2 >> 32) == a.epoch;
+      }
+      if (__all_sync(0xffffffffu, ok)) break;
+      __nanosleep(200);
+      uint32_t stop = 0;
+      if (lane == 0) {
+        if (ctl->abort) stop = 1;
+        else if (clock64() - t0 > kWaitCycles) { atomicOr(status, ANODE_ST_WAIT_PEER); ctl->abort = 1; stop = 1; }
+      }
+      if (__shfl_sync(0xffffffffu, stop, 0)) return false;
+    }
+    // merge in rank order (lane = rank; the shuffle tree is the same on every GPU, so all ranks
+    // obtain bit-identical statistics)
+    const bool live = lane < a.world;
+    const double f0 = live ? (double)__uint_as_float((uint32_t)v0) : 0.0;
+    const double f1 = live ? (double)__uint_as_float((uint32_t)v1) : 0.0;
+    const double f2 = live ? (double)__uint_as_float((uint32_t)v2) : 0.0;
+    if constexpr (DIR == 0) {
+      const double sn = warp_sum_all(f0), sm = warp_sum_all(f0 * f1);
+      const double mean = sm / sn;
+      const double d = f1 - mean;
+      const double sq = warp_sum_all(live ? f2 + f0 * d * d : 0.0);
+      tot = Moments64{sn, mean, sq};
+    } else {
+      s1 = warp_sum_all(f0); s2 = warp_sum_all(f1);
+    }
+  }
   if constexpr (DIR == 0) {
     const float mf = (float)tot.mean;
     const float vf = (float)(tot.m2 / tot.n + (double)a.epsilon);     // biased, epsilon folded in (batch_norm.cu:160)
@@ -820,7 +885,6 @@ __device__ __forceinline__ bool pull_merge_unit(const FusedArgs &a, RingCtl *ctl
       if (a.run_var) { const float o = a.run_var[u]; a.run_var[u] = o + a.avg_rate * (vf - o); }
     }
   } else {
-    s1 = warp_sum_all(s1); s2 = warp_sum_all(s2);
     const float r = inv_std(var_in);
     const double rs2 = (double)r * s2;                       // sum(dz * xhat)
     const double A = (double)gm * (double)r;

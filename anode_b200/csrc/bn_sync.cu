@@ -91,7 +91,19 @@ static size_t gather_bytes(uint32_t C, uint32_t world) { return (size_t)align_up
 static int run_sync(FusedArgs &a, int dir, bool aligned, AnodeSyncComm *comm, size_t fused_ws_bytes, cudaStream_t stream)
 {
   const NcclApi &api = nccl();
-  if (!comm || !api.ok) return ANODE_E_COMM;
+  if (!comm) return ANODE_E_COMM;
+  if (comm->world > 1 && comm->xchg_channels >= a.plan.C && ring_applies(a, dir, aligned)) {
+    // One kernel per direction: the block that owns a channel's first tile stores this GPU's
+    // record into every rank's exchange buffer (plain peer stores over NVLink), every block reads
+    // the records of all ranks from its own GPU's buffer.  No collective call, no extra launches.
+    a.mode = MODE_FUSED;
+    a.rank = (uint32_t)comm->rank; a.world = (uint32_t)comm->world;
+    a.xchg_channels = comm->xchg_channels;
+    a.epoch = ++comm->epoch;
+    for (int r = 0; r < comm->world; ++r) a.xchg[r] = comm->xchg[r];
+    return launch_best(a, dir, aligned, stream);
+  }
+  if (!api.ok) return ANODE_E_COMM;
   // the gather buffer sits behind the single-GPU workspace
   float4 *gathered = reinterpret_cast<float4 *>(a.ws + fused_ws_bytes);
   const Plan base = a.plan;
@@ -138,6 +150,25 @@ extern "C" int anode_gpu_sync_comm_create(const void *unique_id, int rank, int w
   c->rank = rank; c->world = world;
   if (api.CommInitRank(&c->nccl, world, id, rank) != ncclSuccess) { delete c; return ANODE_E_COMM; }
   *out = c;
+  return ANODE_OK;
+}
+
+extern "C" size_t anode_gpu_sync_exchange_bytes(uint32_t max_channels, int world)
+{
+  if (max_channels == 0 || world < 1 || world > 8) return 0;
+  return (size_t)2 * (size_t)world * max_channels * 4 * sizeof(unsigned long long);    // [buffer][source rank][channel][word]
+}
+
+extern "C" int anode_gpu_sync_comm_attach_exchange(struct AnodeSyncComm *comm, void *const *peer_ptrs, uint32_t max_channels)
+{
+  if (!comm || !peer_ptrs) return ANODE_E_NULL;
+  if (comm->world > 8 || max_channels == 0) return ANODE_E_COMM;
+  for (int r = 0; r < comm->world; ++r) {
+    if (!peer_ptrs[r] || (reinterpret_cast<uintptr_t>(peer_ptrs[r]) & 7u)) return ANODE_E_COMM;
+    comm->xchg[r] = static_cast<unsigned long long *>(peer_ptrs[r]);
+  }
+  comm->xchg_channels = max_channels;
+  comm->epoch = 0;
   return ANODE_OK;
 }
 

@@ -435,13 +435,19 @@ class SyncBatchNormRelu(FusedBatchNormRelu):
     """FusedBatchNormRelu over a batch sharded across the ranks of `comm` (anode_b200.sync.SyncComm):
     statistics, running averages, dgamma and dbeta are those of the global batch."""
 
-    launches_per_step = 6      # per direction: reduce kernel, merge kernel, apply kernel (+ one NCCL all-gather)
+    @property
+    def launches_per_step(self):
+        """Two kernels per step with the in-kernel exchange; otherwise, per direction, reduce kernel,
+        merge kernel and apply kernel (plus one NCCL all-gather)."""
+        return 2 if getattr(self.comm, "_exchange", None) is not None else 6
 
-    def __init__(self, channels, comm=None, global_count=None, **kw):
+    def __init__(self, channels, comm=None, global_count=None, exchange=True, **kw):
         super().__init__(channels, **kw)
         if comm is None:
             from .sync import SyncComm
             comm = SyncComm.from_torch_distributed()
+            if exchange and comm.world > 1:
+                comm.attach_exchange(channels)       # one kernel per direction, exchange inside it
         self.comm = comm
         self.global_count = global_count      # elements per channel over all ranks; default: equal shards
 

@@ -75,6 +75,29 @@ class SyncComm:
         check(lib.anode_gpu_sync_comm_create(raw, rank, world, ctypes.byref(handle)), "anode_gpu_sync_comm_create")
         return cls(handle, rank, world)
 
+    def attach_exchange(self, max_channels, group=None):
+        """Collective: allocates a peer-visible exchange buffer on every rank (torch symmetric
+        memory is the allocator and the rendezvous; it is not on the data path) and hands the
+        world's pointers to the C ABI, which switches the synchronized calls to the one-kernel
+        form with the exchange inside the kernel."""
+        import torch
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm
+        lib = _lib.load()
+        nbytes = int(lib.anode_gpu_sync_exchange_bytes(max_channels, self.world))
+        if nbytes == 0:
+            raise ValueError("exchange supports 1..8 ranks")
+        buf = symm.empty(nbytes, dtype=torch.uint8, device=torch.device("cuda", torch.cuda.current_device()))
+        buf.zero_()
+        hdl = symm.rendezvous(buf, group if group is not None else dist.group.WORLD)
+        torch.cuda.synchronize()
+        dist.barrier(group)
+        ptrs = (ctypes.c_void_p * self.world)(*[int(p) for p in hdl.buffer_ptrs])
+        check(lib.anode_gpu_sync_comm_attach_exchange(self.handle, ptrs, max_channels),
+              "anode_gpu_sync_comm_attach_exchange")
+        self._exchange = (buf, hdl)          # keep the mapping alive
+        return self
+
     def destroy(self):
         if self.handle:
             _lib.load().anode_gpu_sync_comm_destroy(self.handle)

@@ -245,7 +245,8 @@ def make_layer(ops, channels, world, gamma, beta):
     if world == 1:
         layer = ops.FusedBatchNormRelu(channels, epsilon=1e-5, avg_rate=0.1, affine=True, relu=True)
     else:
-        layer = ops.SyncBatchNormRelu(channels, epsilon=1e-5, avg_rate=0.1, affine=True, relu=True)
+        layer = ops.SyncBatchNormRelu(channels, epsilon=1e-5, avg_rate=0.1, affine=True, relu=True,
+                                      exchange=os.environ.get("ANODE_BENCH_NCCL_EXCHANGE", "0") != "1")
     layer.gamma.copy_(gamma); layer.beta.copy_(beta)
     return layer
 
@@ -352,7 +353,7 @@ def main():
                 "peak_kind": peak_kind, "traffic": None}
 
     w = WORKLOADS[args.workload]
-    kernel_name = "bn_ring_kernel<%s> (fused reduce+apply)" if world == 1 else \
+    kernel_name = "bn_ring_kernel<%s> (fused reduce+apply)" if main_res["launches_per_step"] == 2 else \
         "reduce kernel + all-gather + merge kernel + apply kernel (%s)"
     line = {
         "metric": "bn_relu_fwd_bwd_elements_per_s", "value": main_res["value"], "unit": "elements/s",
@@ -361,7 +362,8 @@ def main():
         "config": {"workload": args.workload, "global_shape": list(w["shape"]), "local_shape": list(local_shape(w, rank, world)),
                    "sharded_axis": w["axis"], "layout": "NCHW f32, eps=1e-5, avg_rate=0.1, gamma/beta, ReLU",
                    "l2": "inputs larger than L2 (no flush needed)" if main_res["elements_local"] * 4 > 512e6 else "inputs near L2 size",
-                   "parallelism": "syncbn_dp%d" % world},
+                   "parallelism": "syncbn_dp%d" % world,
+                   "exchange": "none" if world == 1 else ("in-kernel peer stores" if main_res["launches_per_step"] == 2 else "nccl all-gather")},
         "per_gpu_value": main_res["value"] / world,
         "fwd_ms": main_res["fwd_ms"], "bwd_ms": main_res["bwd_ms"],
         "roofline": dict(roof(BYTES_BWD, main_res["bwd_ms"]), kernel=kernel_name % "bwd"),

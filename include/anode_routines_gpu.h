@@ -269,6 +269,20 @@ int anode_gpu_sync_get_unique_id(void *out);
 int anode_gpu_sync_comm_create(const void *unique_id, int rank, int world, struct AnodeSyncComm **out);
 int anode_gpu_sync_comm_destroy(struct AnodeSyncComm *comm);
 
+/* Optional: exchange inside the kernels instead of an NCCL all-gather between them.
+ * Every rank allocates a buffer of anode_gpu_sync_exchange_bytes(max_channels, world) bytes that
+ * all ranks of the node can address (peer-mapped / symmetric memory), zeroes it once, and passes
+ * the world's buffers, as mapped into its own address space and indexed by rank, to
+ * anode_gpu_sync_comm_attach_exchange (peer_ptrs[rank] is the local buffer).  From then on the
+ * synchronized calls with dim1 <= max_channels run as ONE kernel per direction: the block that
+ * completes a channel on a GPU stores that GPU's 24-byte record into every rank's buffer with
+ * plain stores over NVLink and all blocks read the records from their own GPU's memory (no
+ * multicast, no loads from peer memory).  Records carry the call's sequence number, so nothing
+ * has to be cleared between calls; all ranks must make the same sequence of synchronized calls.
+ * Waits on peers are bounded (ANODE_ST_WAIT_PEER in the status word). */
+size_t anode_gpu_sync_exchange_bytes(uint32_t max_channels, int world);
+int anode_gpu_sync_comm_attach_exchange(struct AnodeSyncComm *comm, void *const *peer_ptrs, uint32_t max_channels);
+
 /* Scratch for a LOCAL [dim0, dim1, dim2] shard when `world` ranks take part. */
 size_t anode_gpu_sync_batch_norm_workspace_bytes(uint32_t dim0, uint32_t dim1, uint32_t dim2, int world);
 

@@ -17,7 +17,7 @@ pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def _worker(rank, world, port, shape, axis, out_dir, dist_kind):
+def _worker(rank, world, port, shape, axis, out_dir, dist_kind, exchange):
     sys.path.insert(0, ROOT)
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
@@ -31,7 +31,8 @@ def _worker(rank, world, port, shape, axis, out_dir, dist_kind):
     idx = [slice(None)] * len(shape); idx[axis] = slice(lo, hi)
     x = torch.from_numpy(np.ascontiguousarray(d["x"][tuple(idx)])).cuda()
     dy = torch.from_numpy(np.ascontiguousarray(d["dy"][tuple(idx)])).cuda()
-    layer = ops.SyncBatchNormRelu(shape[1], epsilon=1e-5, avg_rate=0.1)
+    layer = ops.SyncBatchNormRelu(shape[1], epsilon=1e-5, avg_rate=0.1, exchange=exchange)
+    assert layer.launches_per_step == (2 if (exchange and world > 1) else 6)
     layer.gamma.copy_(torch.from_numpy(d["gamma"])); layer.beta.copy_(torch.from_numpy(d["beta"]))
     for _ in range(2):                      # twice: the workspace must come back clean
         layer.avg_mean.zero_(); layer.avg_var.fill_(1.0)
@@ -51,9 +52,9 @@ CASES = [((16, 8, 28, 28), 0, "normal"), ((8, 4, 8, 16, 16), 2, "normal"), ((32,
          ((6, 3, 5, 5), 0, "normal")]
 
 
-def _run(tmp_path, world, shape, axis, dist_kind):
+def _run(tmp_path, world, shape, axis, dist_kind, exchange=True):
     port = 30000 + (os.getpid() * 7 + hash((shape, axis, world)) % 997) % 3000
-    mp.spawn(_worker, args=(world, port, shape, axis, str(tmp_path), dist_kind), nprocs=world, join=True)
+    mp.spawn(_worker, args=(world, port, shape, axis, str(tmp_path), dist_kind, exchange), nprocs=world, join=True)
     d = make_inputs(shape, seed=41, dist=dist_kind, loc=0.5 if dist_kind == "normal" else 0.0,
                     scale=2.0 if dist_kind == "normal" else 4.0)
     truth = o.bn_relu_fwd_bwd_f64(d["x"], d["dy"], 1e-5, 0.1, d["run_mean"], d["run_var"], d["gamma"], d["beta"])
@@ -73,6 +74,7 @@ def test_sync_world1_matches_oracle(tmp_path, shape, axis, dist_kind):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+@pytest.mark.parametrize("exchange", [True, False], ids=["in-kernel-exchange", "nccl-all-gather"])
 @pytest.mark.parametrize("shape,axis,dist_kind", CASES)
-def test_sync_world2_matches_oracle(tmp_path, shape, axis, dist_kind):
-    _run(tmp_path, 2, shape, axis, dist_kind)
+def test_sync_world2_matches_oracle(tmp_path, shape, axis, dist_kind, exchange):
+    _run(tmp_path, 2, shape, axis, dist_kind, exchange)
