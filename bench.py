@@ -93,13 +93,14 @@ def gen_local(w, rank, world, device):
 
 
 class ClockSampler:
-    """nvidia-smi in the background while the timed region runs."""
-    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+    """nvidia-smi in the background.  It is started before the warm-up (it needs a few hundred ms to
+    produce its first line) and its time-stamped samples are filtered to the timed region."""
+    Q = ("timestamp,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
          "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
          "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, index):
-        self.index, self.p = index, None
+        self.index, self.p, self.t0, self.t1 = index, None, None, None
 
     def start(self):
         try:
@@ -109,29 +110,44 @@ class ClockSampler:
         except Exception:
             self.p = None
 
+    def begin(self):
+        self.t0 = time.time()
+
+    def end(self):
+        self.t1 = time.time()
+
     def stop(self):
+        import datetime
         if self.p is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.05)
         self.p.terminate()
         try:
             out, _ = self.p.communicate(timeout=5)
         except Exception:
             self.p.kill(); out = ""
-        sm, mx, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        rows = []
         for line in out.splitlines():
-            f = [s.strip() for s in line.split(",")]
+            f = [x.strip() for x in line.split(",")]
             if len(f) < 9:
                 continue
             try:
-                sm.append(float(f[1])); mx.append(float(f[2]))
+                ts = datetime.datetime.strptime(f[0], "%Y/%m/%d %H:%M:%S.%f").timestamp()
+                rows.append((ts, float(f[1]), float(f[2]), [n for n, v in zip(names, f[5:9]) if v.lower().startswith("active")]))
             except ValueError:
                 continue
-            for n, v in zip(names, f[5:9]):
-                if v.lower().startswith("active"):
-                    reasons.add(n)
+        inside = [r for r in rows if self.t0 is not None and self.t0 <= r[0] <= self.t1]
+        window = "timed region"
+        if not inside and rows and self.t0 is not None:
+            # region shorter than the sampling period: take the samples closest to it
+            mid = 0.5 * (self.t0 + self.t1)
+            inside = sorted(rows, key=lambda r: abs(r[0] - mid))[:3]
+            window = "3 samples nearest to the timed region (region shorter than the 20 ms sampling period)"
+        sm = [r[1] for r in inside]; mx = [r[2] for r in inside]
+        reasons = sorted({n for r in inside for n in r[3]})
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "samples": len(sm), "reasons": sorted(reasons)}
+                "samples": len(sm), "window": window, "reasons": reasons}
 
 
 def cpu_baseline(w, steps=3, warmup=0, seconds_hint=20.0):
@@ -215,6 +231,8 @@ def time_layer(layer, x, dy, y, dx, steps, warmup, dist, sampler=None):
     """W warm-up steps, then K timed steps bracketed by barrier + synchronize; device time by CUDA
     events on the launching stream; per-kernel events inside.  Returns (total_ms, fwd_ms, bwd_ms)."""
     import torch
+    if sampler:
+        sampler.start()
     for _ in range(warmup):
         layer.forward(x, out=y); layer.backward(dy, out=dx)
     torch.cuda.synchronize()
@@ -223,7 +241,7 @@ def time_layer(layer, x, dy, y, dx, steps, warmup, dist, sampler=None):
     torch.cuda.synchronize()
     ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(steps)]
     if sampler:
-        sampler.start()
+        sampler.begin()
     for i in range(steps):
         ev[i][0].record()
         layer.forward(x, out=y)
@@ -234,6 +252,8 @@ def time_layer(layer, x, dy, y, dx, steps, warmup, dist, sampler=None):
     if dist is not None:
         dist.barrier()
     torch.cuda.synchronize()
+    if sampler:
+        sampler.end()
     clocks = sampler.stop() if sampler else None
     total = ev[0][0].elapsed_time(ev[-1][2])
     fwd = sum(e[0].elapsed_time(e[1]) for e in ev) / steps
