@@ -53,6 +53,10 @@ SIGNATURES = {
         (c_int, _D + [c_int, c_int] + [vp] * 9 + [vp, size_t] + _T),
     "anode_gpu_batch_norm_relu_fused_fwd_static_3d1_packed_f32":
         (c_int, _D + [f32, f32, c_int] + [vp] * 8 + _T),
+    "anode_gpu_batch_norm_host_step_staging_bytes": (size_t, _D + [u32]),
+    "anode_gpu_batch_norm_host_step_blocks": (u32, _D + [u32]),
+    "anode_gpu_batch_norm_relu_fused_step_host_3d1_packed_f32":
+        (c_int, _D + [f32, f32, c_int] + [vp] * 12 + [vp, size_t, u32] + _T),
     "anode_gpu_online_average_f32": (c_int, [u32, f32, vp, vp] + _T),
     "anode_gpu_sync_unique_id_bytes": (size_t, []),
     "anode_gpu_sync_get_unique_id": (c_int, [vp]),

@@ -169,6 +169,25 @@ int launch_ring(FusedArgs &a, const RingGeom &g, int dir, cudaStream_t stream)
   return ANODE_OK;
 }
 
+// The caller's workspace holds two independent parts, one per direction (forward first): a
+// direction's kernels keep state in their part from launch to launch (which partial buffer is
+// current, words waiting to be cleared), laid out by that direction's own tile plan, so forward
+// and backward launches must not share one.  The status word is the first word of the whole.
+uint64_t workspace_part_bytes(uint32_t dim0, uint32_t C, uint32_t N)
+{
+  // the plan depends on pointer alignment, which is not known yet: cover both cases
+  const Plan a = plan_for(dim0, C, N, true), b = plan_for(dim0, C, N, false);
+  uint64_t need = a.ws_bytes > b.ws_bytes ? a.ws_bytes : b.ws_bytes;
+  for (int dir = 0; dir < 2; ++dir) {
+    Plan rp; RingGeom g;
+    if (ring_plan_for(dim0, C, N, true, dir, rp, g) && rp.ws_bytes > need) need = rp.ws_bytes;
+  }
+#ifdef ANODE_RING_PROFILE
+  need += 1u << 20;     // room for the per-block cycle counters
+#endif
+  return align_up_u64(need, 256);
+}
+
 // Bytes at the start of a workspace that hold progress counters, flags and records, i.e. what has
 // to be zero when a launch begins (the per-tile partials behind them are written before they are read).
 uint64_t control_region_bytes(uint32_t dim0, uint32_t C, uint32_t N, bool aligned)
@@ -267,8 +286,10 @@ int prepare_fwd(FusedArgs &a, uint32_t dim0, uint32_t dim1, uint32_t dim2, float
   if (!ws || !aligned16(ws)) return ANODE_E_WORKSPACE;
   a = FusedArgs{};
   a.plan = plan_for(dim0, dim1, dim2, aligned16(x) && aligned16(y));
-  if (ws_bytes < a.plan.ws_bytes) return ANODE_E_WORKSPACE;
-  a.ws_capacity = ws_bytes;
+  const uint64_t part = workspace_part_bytes(dim0, dim1, dim2);
+  if (ws_bytes < part) return ANODE_E_WORKSPACE;              // forward uses the first part only
+  a.ws_capacity = part;
+  a.status = static_cast<uint32_t *>(ws);
   a.x = x; a.gamma = gamma; a.beta = beta; a.out = y;
   a.mean = mean; a.var = var; a.run_mean = run_mean; a.run_var = run_var;
   a.ws = static_cast<unsigned char *>(ws);
@@ -289,11 +310,13 @@ int prepare_bwd(FusedArgs &a, uint32_t dim0, uint32_t dim1, uint32_t dim2, int r
   if (!ws || !aligned16(ws)) return ANODE_E_WORKSPACE;
   a = FusedArgs{};
   a.plan = plan_for(dim0, dim1, dim2, aligned16(x) && aligned16(dy) && aligned16(dx));
-  if (ws_bytes < a.plan.ws_bytes) return ANODE_E_WORKSPACE;
-  a.ws_capacity = ws_bytes;
+  const uint64_t part = workspace_part_bytes(dim0, dim1, dim2);
+  if (ws_bytes < 2 * part) return ANODE_E_WORKSPACE;
+  a.ws_capacity = part;
+  a.status = static_cast<uint32_t *>(ws);
   a.x = x; a.dy = dy; a.gamma = gamma; a.beta = beta; a.mean_in = mean; a.var_in = var;
   a.out = dx; a.dgamma = dgamma; a.dbeta = dbeta;
-  a.ws = static_cast<unsigned char *>(ws);
+  a.ws = static_cast<unsigned char *>(ws) + part;              // the backward part
   a.relu = relu ? 1u : 0u; a.accumulate = accumulate ? 1u : 0u;
   a.mode = MODE_FUSED;
   a.count_total = (double)dim0 * (double)dim2;
@@ -315,17 +338,7 @@ using namespace anode_b200;
 extern "C" size_t anode_gpu_batch_norm_fused_workspace_bytes(uint32_t dim0, uint32_t dim1, uint32_t dim2)
 {
   if (check_dims(dim0, dim1, dim2)) return 0;
-  // the plan depends on pointer alignment, which is not known yet: cover both cases
-  const Plan a = plan_for(dim0, dim1, dim2, true), b = plan_for(dim0, dim1, dim2, false);
-  uint64_t need = a.ws_bytes > b.ws_bytes ? a.ws_bytes : b.ws_bytes;
-  for (int dir = 0; dir < 2; ++dir) {
-    Plan rp; RingGeom g;
-    if (ring_plan_for(dim0, dim1, dim2, true, dir, rp, g) && rp.ws_bytes > need) need = rp.ws_bytes;
-  }
-#ifdef ANODE_RING_PROFILE
-  need += 1u << 20;     // room for the per-block cycle counters
-#endif
-  return (size_t)need;
+  return (size_t)(2 * workspace_part_bytes(dim0, dim1, dim2));
 }
 
 extern "C" int anode_gpu_batch_norm_fused_workspace_init(void *workspace, size_t bytes, struct CUstream_st *stream)
@@ -357,6 +370,7 @@ extern "C" int anode_gpu_batch_norm_relu_fused_fwd_3d1_packed_f32(
   const int rc = prepare_fwd(a, dim0, dim1, dim2, epsilon, avg_rate, relu, x, gamma, beta, y, mean, var,
                              run_mean, run_var, workspace, workspace_bytes);
   if (rc) return rc;
+  if (workspace_bytes < anode_gpu_batch_norm_fused_workspace_bytes(dim0, dim1, dim2)) return ANODE_E_WORKSPACE;
   return launch_best(a, 0, aligned16(x) && aligned16(y), stream);
 }
 

@@ -36,7 +36,8 @@ struct FusedArgs {
   float *mean, *var, *run_mean, *run_var;   // forward outputs
   float *dgamma, *dbeta;   // backward outputs
   unsigned char *ws;
-  uint64_t ws_capacity;    // bytes the caller provided
+  uint64_t ws_capacity;    // bytes of this direction's part of the workspace
+  uint32_t *status;        // the workspace's status word (first word of the caller's buffer)
   float epsilon, avg_rate;
   uint32_t relu, accumulate, mode;
   uint32_t use_rec;        // publish tagged records (the warp-specialised kernel reads them)
@@ -624,7 +625,7 @@ __global__ void __launch_bounds__(kThreads) bn_pipeline_kernel(const FusedArgs a
   const uint32_t my_tiles = (b < P.total_tiles) ? (P.total_tiles - b + G - 1) / G : 0;
   const uint32_t look = (a.mode == MODE_FUSED) ? P.lookahead_steps : 0;
   const bool do_reduce = a.mode != MODE_APPLY, do_apply = a.mode != MODE_STATS;
-  uint32_t *status = ws_u32(a, 0);
+  uint32_t *status = a.status;
   uint32_t *done = ws_u32(a, P.off_done), *ready = ws_u32(a, P.off_ready), *applied = ws_u32(a, P.off_applied);
 
   for (uint32_t s = 0; s < my_tiles + look; ++s) {

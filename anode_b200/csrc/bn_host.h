@@ -45,6 +45,7 @@ int launch_pipeline(FusedArgs &a, int dir, cudaStream_t stream);
 // picks the warp-specialised kernel where it applies, the plain one otherwise
 int launch_best(FusedArgs &a, int dir, bool aligned, cudaStream_t stream);
 bool ring_applies(const FusedArgs &a, int dir, bool aligned);
+uint64_t workspace_part_bytes(uint32_t dim0, uint32_t C, uint32_t N);
 uint64_t control_region_bytes(uint32_t dim0, uint32_t C, uint32_t N, bool aligned);
 
 }  // namespace anode_b200

@@ -909,7 +909,7 @@ __global__ void __launch_bounds__(kRingThreads, 1) bn_ring_kernel(const FusedArg
   RingCtl *ctl = reinterpret_cast<RingCtl *>(sm);
   const Plan &P = a.plan;
   const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  uint32_t *status = ws_u32(a, 0);
+  uint32_t *status = a.status;
   uint32_t *exit_ctr = ws_u32(a, 4);
   uint32_t *done = ws_u32(a, P.off_done);
 

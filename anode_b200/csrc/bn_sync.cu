@@ -105,7 +105,7 @@ static int run_sync(FusedArgs &a, int dir, bool aligned, AnodeSyncComm *comm, si
   }
   if (!api.ok) return ANODE_E_COMM;
   // the gather buffer sits behind the single-GPU workspace
-  float4 *gathered = reinterpret_cast<float4 *>(a.ws + fused_ws_bytes);
+  float4 *gathered = reinterpret_cast<float4 *>(reinterpret_cast<unsigned char *>(a.status) + fused_ws_bytes);
   const Plan base = a.plan;
   a.mode = MODE_STATS;
   int rc = launch_best(a, dir, aligned, stream);

@@ -37,6 +37,11 @@ def _stream(stream):
     return ctypes.c_void_p(s.cuda_stream)
 
 
+def _hp(t):
+    """Pointer to a host tensor's data."""
+    return ctypes.c_void_p(t.data_ptr())
+
+
 def _p(t):
     if t is None:
         return None
@@ -373,6 +378,7 @@ class FusedBatchNormRelu:
         self.dgamma = torch.zeros(channels, device=dev) if affine else None
         self.dbeta = torch.zeros(channels, device=dev) if affine else None
         self._ws = None
+        self._staging = None
         self._x = None
 
     launches_per_step = 2      # one forward kernel, one backward kernel
@@ -387,16 +393,44 @@ class FusedBatchNormRelu:
         """Device status word of the last launches (0 = clean); synchronises the stream."""
         return 0 if self._ws is None else self._ws.status()
 
-    def step_from_host(self, hx, hdy, hy, hdx, x, dy, y, dx):
-        """One forward + backward with the tensors in (pinned) host memory: copies x and dy to
-        the device buffers, runs both kernels, copies y and dx back.  Everything is enqueued on
-        the current stream; the caller synchronises."""
-        x.copy_(hx, non_blocking=True)
-        dy.copy_(hdy, non_blocking=True)
-        self.forward(x, out=y)
-        self.backward(dy, out=dx)
-        hy.copy_(y, non_blocking=True)
-        hdx.copy_(dx, non_blocking=True)
+    def step_from_host(self, hx, hdy, hy, hdx, chunk_channels=0):
+        """One forward + backward with x, dy, y, dx in (page-locked) host memory.  The layer is
+        processed in blocks of channels, so that copies to the device, both kernels and copies back
+        overlap; everything is enqueued when the call returns and the current stream ends after
+        the last copy.  Returns the number of channel blocks (each is two kernel launches)."""
+        for t in (hx, hdy, hy, hdx):
+            if t.is_cuda or not t.is_contiguous() or t.dtype != torch.float32:
+                raise ValueError("step_from_host takes contiguous float32 host tensors")
+        d0, c, n = dims_of(hx)
+        lib = _lib.load()
+        need = int(lib.anode_gpu_batch_norm_host_step_staging_bytes(d0, c, n, int(chunk_channels)))
+        if need == 0:
+            raise AnodeError(-2, "anode_gpu_batch_norm_host_step_staging_bytes")
+        dev = self.mean.device
+        if self._staging is None or self._staging.numel() < need:
+            self._staging = None
+            self._staging = torch.empty(need, dtype=torch.uint8, device=dev)
+        check(lib.anode_gpu_batch_norm_relu_fused_step_host_3d1_packed_f32(
+            d0, c, n, ctypes.c_float(self.epsilon), ctypes.c_float(self.avg_rate), int(self.relu),
+            _hp(hx), _hp(hdy), _p(self.gamma), _p(self.beta), _hp(hy), _hp(hdx),
+            _p(self.mean), _p(self.var), _p(self.avg_mean), _p(self.avg_var), _p(self.dgamma), _p(self.dbeta),
+            ctypes.c_void_p(self._staging.data_ptr()), need, int(chunk_channels), _cfg(None), _stream(None)),
+            "anode_gpu_batch_norm_relu_fused_step_host_3d1_packed_f32")
+        return self.host_step_blocks(d0, c, n, chunk_channels)
+
+    @staticmethod
+    def host_step_blocks(d0, c, n, chunk_channels=0):
+        """Channel blocks step_from_host cuts a [d0, c, n] layer into."""
+        return int(_lib.load().anode_gpu_batch_norm_host_step_blocks(d0, c, n, int(chunk_channels)))
+
+    def host_step_status(self):
+        """Status word of the last step_from_host (0 = clean); synchronises the stream."""
+        if self._staging is None:
+            return 0
+        out = ctypes.c_uint32(0)
+        check(_lib.load().anode_gpu_batch_norm_fused_status(
+            ctypes.c_void_p(self._staging.data_ptr()), _stream(None), ctypes.byref(out)), "status")
+        return int(out.value)
 
     def forward(self, x, out=None):
         axes = list(range(x.dim() - 2))
@@ -440,6 +474,10 @@ class SyncBatchNormRelu(FusedBatchNormRelu):
         """Two kernels per step with the in-kernel exchange; otherwise, per direction, reduce kernel,
         merge kernel and apply kernel (plus one NCCL all-gather)."""
         return 2 if getattr(self.comm, "_exchange", None) is not None else 6
+
+    def step_from_host(self, *args, **kw):
+        raise NotImplementedError("the host-buffer step cuts the layer by channels on one GPU; "
+                                  "shard the host batch and call forward/backward instead")
 
     def __init__(self, channels, comm=None, global_count=None, exchange=True, **kw):
         super().__init__(channels, **kw)

@@ -180,7 +180,8 @@ void anode_gpu_positive_clip_flat_map_bwd_f32(
 #define ANODE_ST_ABORTED      4u  /* some block saw the bits above and skipped work */
 
 /* Scratch the fused kernels need for a [dim0, dim1, dim2] problem: per-tile partial
- * statistics, per-channel coefficients, progress counters.  A few hundred KB. */
+ * statistics, per-channel coefficients, progress counters; one part per direction (each
+ * direction keeps state in its part from launch to launch).  A few hundred KB to a few MB. */
 size_t anode_gpu_batch_norm_fused_workspace_bytes(uint32_t dim0, uint32_t dim1, uint32_t dim2);
 
 /* Zeroes a workspace (cudaMemsetAsync on `stream`).  Needed once after allocation and after
@@ -241,6 +242,33 @@ int anode_gpu_batch_norm_relu_fused_fwd_static_3d1_packed_f32(
     float epsilon, float avg_rate, int relu,
     const float *x, const float *gamma, const float *beta,
     float *y, float *mean, float *var, float *run_mean, float *run_var,
+    const struct KernelConfig *cfg, struct CUstream_st *stream);
+
+/* Forward + backward of one layer whose tensors are in HOST memory (no counterpart in the
+ * reference, which moves whole arrays with separate copies: MemArray4d -> device array,
+ * tests/test_gpu.rs:138-160).  host_x, host_dy, host_y, host_dx are packed [dim0, dim1, dim2]
+ * host tensors, page-locked for the copies to overlap; every other pointer is a device pointer as
+ * in the two calls above (mean, var, dgamma, dbeta ... are [dim1]).  The layer is processed in
+ * blocks of `chunk_channels` channels (0 = let the library choose): block k+1 is copied to the
+ * device while block k is computed and block k-1 is copied back, so both directions of the link
+ * are busy at once.  `staging` is device memory of anode_gpu_batch_norm_host_step_staging_bytes
+ * bytes, 256-byte aligned, contents irrelevant (it also holds the workspace; its first word is the
+ * status word anode_gpu_batch_norm_fused_status reads).  Kernels run on `stream`, copies on two
+ * streams the library creates once per device; when the call returns everything is enqueued and
+ * `stream` ends after the last copy.  Make the first call on a device outside of stream capture.
+ * host_y may be host_x and host_dx may be host_dy. */
+size_t anode_gpu_batch_norm_host_step_staging_bytes(uint32_t dim0, uint32_t dim1, uint32_t dim2,
+                                                    uint32_t chunk_channels);
+/* Number of channel blocks the call below cuts the layer into (two kernel launches each). */
+uint32_t anode_gpu_batch_norm_host_step_blocks(uint32_t dim0, uint32_t dim1, uint32_t dim2,
+                                               uint32_t chunk_channels);
+int anode_gpu_batch_norm_relu_fused_step_host_3d1_packed_f32(
+    uint32_t dim0, uint32_t dim1, uint32_t dim2,
+    float epsilon, float avg_rate, int relu,
+    const float *host_x, const float *host_dy, const float *gamma, const float *beta,
+    float *host_y, float *host_dx,
+    float *mean, float *var, float *run_mean, float *run_var, float *dgamma, float *dbeta,
+    void *staging, size_t staging_bytes, uint32_t chunk_channels,
     const struct KernelConfig *cfg, struct CUstream_st *stream);
 
 /* Running-statistic update on its own (OnlineAverageOp, src/ops_gpu.rs:6034-6077; rule

@@ -123,6 +123,20 @@ def test_workspace_reuse_inplace_and_accumulate(ops):
     assert ws.status() == 0
 
 
+def test_consecutive_steps_with_new_data_share_one_workspace(ops):
+    """Training: the same layer and workspace, different data every step.  The two directions tile
+    this shape differently, so state either of them leaves in the workspace must not reach the other
+    (or its own next launch)."""
+    shape = (64, 32, 56, 56)
+    ws = None
+    for step in range(3):
+        d = make_inputs(shape, seed=100 + step, loc=0.3 * step, scale=1.0 + step)
+        got, ws = run_fused(ops, d, ws=ws)
+        truth = o.bn_relu_fwd_bwd_f64(d["x"], d["dy"], 1e-5, 0.1, d["run_mean"], d["run_var"],
+                                      d["gamma"], d["beta"])
+        check_layer(got, truth, d["x"], d["gamma"], d["beta"], what="step %d " % step)
+
+
 def test_misaligned_pointers_take_the_scalar_path(ops):
     shape = (4, 4, 8, 8)
     d = make_inputs(shape, seed=12)
