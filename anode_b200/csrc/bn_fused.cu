@@ -38,6 +38,7 @@ const Tunables &tunables()
       env_u32("ANODE_B200_RING_BLOCKS_PER_SM", 1),
       env_u32("ANODE_B200_RING_WARPS_FWD", 8),
       env_u32("ANODE_B200_RING_WARPS_BWD", 16),
+      env_u32("ANODE_B200_SEGRES", 1),
   };
   return t;
 }
@@ -215,6 +216,7 @@ int launch_best(FusedArgs &a, int dir, bool aligned, cudaStream_t stream)
     a.plan = rp;
     return launch_ring(a, g, dir, stream);
   }
+  if (tunables().segres && segres_applies(a, dir, aligned) && launch_segres(a, dir, stream) == ANODE_OK) return ANODE_OK;
   return launch_pipeline(a, dir, stream);
 }
 
@@ -398,6 +400,19 @@ extern "C" int anode_gpu_online_average_f32(uint32_t len, float rate, const floa
   online_average_kernel<<<blocks, 256, 0, stream>>>(len, rate, x, y);
   if (cudaGetLastError() != cudaSuccess) return ANODE_E_LAUNCH;
   return ANODE_OK;
+}
+
+// Which kernel serves direction `dir` of a [dim0, dim1, dim2] call with 16-byte aligned tensors on
+// one GPU: 1 = warp-specialised tiled kernel, 2 = cluster kernel for short rows, 0 = plain kernel.
+extern "C" int anode_gpu_batch_norm_fused_kernel_kind(uint32_t dim0, uint32_t dim1, uint32_t dim2, int dir)
+{
+  if (check_dims(dim0, dim1, dim2)) return ANODE_E_DIMS;
+  Plan rp; RingGeom g;
+  if (ring_plan_for(dim0, dim1, dim2, true, dir, rp, g)) return 1;
+  FusedArgs a{};
+  a.plan.dim0 = dim0; a.plan.C = dim1; a.plan.N = dim2; a.mode = MODE_FUSED;
+  if (tunables().segres && segres_applies(a, dir, true)) return 2;
+  return 0;
 }
 
 // ---- diagnostics: the tile plan, for tests of the index arithmetic (no GPU needed) ----------

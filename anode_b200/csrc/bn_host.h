@@ -26,6 +26,7 @@ struct Tunables {
   uint32_t ring_blocks_per_sm;
   uint32_t ring_warps_fwd;  // consumer warps of the forward kernel (8 or 16)
   uint32_t ring_warps_bwd;  // consumer warps of the backward kernel (8 or 16)
+  uint32_t segres;          // 1: use the cluster kernel for short rows where it applies
 };
 const Tunables &tunables();
 
@@ -45,6 +46,9 @@ int launch_pipeline(FusedArgs &a, int dir, cudaStream_t stream);
 // picks the warp-specialised kernel where it applies, the plain one otherwise
 int launch_best(FusedArgs &a, int dir, bool aligned, cudaStream_t stream);
 bool ring_applies(const FusedArgs &a, int dir, bool aligned);
+// the cluster kernel for short rows (bn_segres.cu)
+bool segres_applies(const FusedArgs &a, int dir, bool aligned);
+int launch_segres(FusedArgs &a, int dir, cudaStream_t stream);
 uint64_t workspace_part_bytes(uint32_t dim0, uint32_t C, uint32_t N);
 uint64_t control_region_bytes(uint32_t dim0, uint32_t C, uint32_t N, bool aligned);
 

@@ -1,0 +1,417 @@
+// Fused batch-norm (+ReLU) for short rows: the "segments" shapes (dim0 < 256 or rows that are not
+// 16-byte aligned one by one, e.g. [N, 2048, 7, 7]), where a channel's data is N short runs far
+// apart and the tiled kernels spend more time on bookkeeping than on data.
+//
+// Decomposition: a unit is a block of cb channels, i.e. per sample one contiguous, 16-byte aligned
+// run of L = cb*dim0 floats.  A thread-block CLUSTER of CL blocks owns one unit; block r of the
+// cluster takes the samples [r*Rb, (r+1)*Rb) and copies its [Rb x L] slice into shared memory
+// (cp.async, 16 bytes per request).  Everything else happens on chip:
+//   1. per-column sums over the slice's samples (each thread keeps one float4 column in registers),
+//      shifted by the column's first value;
+//   2. columns -> channels inside the block (fixed order, double precision);
+//   3. the CL block partials are exchanged through distributed shared memory, every block merges
+//      them in rank order (bit-identical coefficients everywhere), block 0 writes the channel outputs;
+//   4. y (or dx) is computed from the slice still in shared memory and streamed out.
+// x (and dy) are read from HBM exactly once, nothing depends on L2 residency, there is no global
+// scratch, no flag and no spin-wait: the only synchronisation is the hardware cluster barrier.
+// Two blocks share an SM, so one block's copies overlap the other's arithmetic.
+//
+// Reference kernels this replaces on such shapes: routines_gpu/batch_norm.cu:24-57, 125-163,
+// 314-336 (forward) and :181-206, 240-280, 354-376, 408-444, 476-515 (backward), with the ReLU of
+// routines_gpu/flat_map.cu:172-194 folded in.
+#include <cooperative_groups.h>
+#include <stdio.h>
+
+#include "bn_device.cuh"
+#include "bn_host.h"
+
+namespace cg = cooperative_groups;
+
+namespace anode_b200 {
+
+#ifndef ANODE_SEG_THREADS
+#define ANODE_SEG_THREADS 256
+#endif
+constexpr uint32_t kSegThreads = ANODE_SEG_THREADS;
+constexpr uint32_t kSegColFloats = 4 * kSegThreads;      // per-column results of one block (x2 arrays)
+constexpr uint32_t kSegMaxCluster = 16;
+
+struct SegGeom {
+  uint32_t cb;          // channels per unit
+  uint32_t cluster;     // blocks per unit
+  uint32_t rows;        // samples per block
+  uint32_t units;
+  uint32_t stages;      // 1: one unit per cluster, several blocks per SM; 2: persistent, next unit's copies in flight
+  uint32_t off_col, off_coef, off_part, off_stage, stage_bytes, off_dy, smem_bytes;
+};
+
+__device__ __forceinline__ void cp_async16(void *smem_dst, const void *gsrc)
+{
+  const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_but_one() { asm volatile("cp.async.wait_group 1;" ::: "memory"); }
+
+// The cluster walks the units cid, cid + clusters, ... (with one stage the grid has a cluster per
+// unit and the loop runs once).  With two stages each block keeps two slices in shared memory: the
+// one being worked on and the next unit's, whose copies are in flight meanwhile.
+template <int DIR>
+__global__ void __launch_bounds__(kSegThreads) bn_segres_kernel(const FusedArgs a, const SegGeom g)
+{
+  extern __shared__ __align__(16) unsigned char sm[];
+  cg::cluster_group cluster = cg::this_cluster();
+  const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const uint32_t rank = cluster.block_rank();
+  const uint32_t cid = blockIdx.x / g.cluster, ncl = gridDim.x / g.cluster;
+  const uint32_t dim0 = a.plan.dim0, C = a.plan.C, N = a.plan.N;
+  const uint32_t n0 = rank * g.rows;
+  const uint32_t rows = n0 < N ? ((N - n0 < g.rows) ? (N - n0) : g.rows) : 0;
+  const uint64_t rs = (uint64_t)C * dim0;
+  const bool relu = a.relu != 0, acc = a.accumulate != 0;
+
+  float *colA = reinterpret_cast<float *>(sm + g.off_col), *colB = colA + kSegColFloats;
+  float *coef = reinterpret_cast<float *>(sm + g.off_coef);         // 8 floats per channel
+  float4 *parts = reinterpret_cast<float4 *>(sm + g.off_part);      // two buffers of one per channel
+
+  // slice of unit u -> stage st, dense [rows][Lw]
+  auto issue = [&](uint32_t u, uint32_t st) {
+    const uint32_t c0 = u * g.cb, cw = (C - c0 < g.cb) ? (C - c0) : g.cb;
+    const uint32_t L4 = cw * dim0 / 4;
+    float *sx = reinterpret_cast<float *>(sm + g.off_stage + (size_t)st * g.stage_bytes);
+    float *sdy = reinterpret_cast<float *>(sm + g.off_stage + (size_t)st * g.stage_bytes + g.off_dy);
+    const uint32_t total4 = rows * L4;
+    const uint32_t row = tid / L4;
+    uint32_t col = tid - row * L4;
+    const uint32_t drow = kSegThreads / L4, dcol = kSegThreads - drow * L4;
+    // float offset of this thread's next piece; advancing by kSegThreads pieces moves drow samples
+    // down and dcol pieces right, wrapping into the next sample
+    size_t off = (size_t)n0 * rs + (size_t)c0 * dim0 + (size_t)row * rs + 4 * (size_t)col;
+    const size_t step = (size_t)drow * rs + 4 * (size_t)dcol, wrap = rs - 4 * (size_t)L4;
+#pragma unroll 5
+    for (uint32_t i = tid; i < total4; i += kSegThreads) {
+      cp_async16(sx + 4 * (size_t)i, a.x + off);
+      if (DIR == 1) cp_async16(sdy + 4 * (size_t)i, a.dy + off);
+      off += step; col += dcol;
+      if (col >= L4) { col -= L4; off += wrap; }
+    }
+  };
+
+  if (cid < g.units) issue(cid, 0);
+  cp_async_commit();
+  uint32_t j = 0;
+  for (uint32_t u = cid; u < g.units; u += ncl, ++j) {
+    const uint32_t st = g.stages == 2 ? (j & 1u) : 0u;
+    const uint32_t c0 = u * g.cb, cw = (C - c0 < g.cb) ? (C - c0) : g.cb;
+    const uint32_t Lw = cw * dim0, L4 = Lw / 4;                     // floats / float4s per sample in this unit
+    const float *sx = reinterpret_cast<const float *>(sm + g.off_stage + (size_t)st * g.stage_bytes);
+    const float *sdy = reinterpret_cast<const float *>(sm + g.off_stage + (size_t)st * g.stage_bytes + g.off_dy);
+    float4 *part = parts + (size_t)st * g.cb;
+
+    // the next unit's slice starts travelling now (its stage was released at the end of the last round)
+    if (g.stages == 2 && u + ncl < g.units) issue(u + ncl, st ^ 1u);
+    cp_async_commit();
+    if (DIR == 1) {
+      // what the mask needs is known before the sums: (mean, gamma*rstd, beta)
+      for (uint32_t ci = tid; ci < cw; ci += kSegThreads) {
+        const uint32_t c = c0 + ci;
+        const float gm = a.gamma ? a.gamma[c] : 1.0f;
+        coef[8 * ci + 0] = a.mean_in[c];
+        coef[8 * ci + 1] = gm * inv_std(a.var_in[c]);
+        coef[8 * ci + 2] = (a.gamma && a.beta) ? a.beta[c] : 0.0f;
+      }
+    }
+    cp_async_wait_but_one();          // everything but the copies issued just above has landed
+    __syncthreads();
+
+    // ---- per-column sums.  Thread (grp, v): float4 column v, samples grp, grp+G, ...
+    const uint32_t G = kSegThreads / L4;                              // >= 1: L4 <= kSegThreads by construction
+    const uint32_t grp = tid / L4, v = tid - grp * L4;
+    const bool active = grp < G;
+    uint32_t ch[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) ch[i] = active ? (4 * v + i) / dim0 : 0;
+    if (active) {
+      const float *px = sx + 4 * (size_t)v;
+      if (DIR == 0) {
+        float K[4] = {0.f, 0.f, 0.f, 0.f}, s[4] = {0.f, 0.f, 0.f, 0.f}, q[4] = {0.f, 0.f, 0.f, 0.f};
+        uint32_t cnt = 0;
+        if (grp < rows) {
+          const float4 p = *reinterpret_cast<const float4 *>(px + (size_t)grp * Lw);
+          K[0] = p.x; K[1] = p.y; K[2] = p.z; K[3] = p.w;
+        }
+        for (uint32_t r = grp; r < rows; r += G) {
+          const float4 p = *reinterpret_cast<const float4 *>(px + (size_t)r * Lw);
+          const float e[4] = {p.x, p.y, p.z, p.w};
+#pragma unroll
+          for (int i = 0; i < 4; ++i) { const float d = e[i] - K[i]; s[i] += d; q[i] = fmaf(d, d, q[i]); }
+          ++cnt;
+        }
+        const float inv = cnt ? __fdividef(1.0f, (float)cnt) : 0.f;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          colA[grp * Lw + 4 * v + i] = fmaf(s[i], inv, K[i]);                         // mean of the column part
+          colB[grp * Lw + 4 * v + i] = fmaxf(q[i] - s[i] * s[i] * inv, 0.f);          // its M2
+        }
+      } else {
+        const float *pd = sdy + 4 * (size_t)v;
+        float cm[4], cs[4], cbt[4], s1[4] = {0.f, 0.f, 0.f, 0.f}, s2[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { cm[i] = coef[8 * ch[i] + 0]; cs[i] = coef[8 * ch[i] + 1]; cbt[i] = coef[8 * ch[i] + 2]; }
+        for (uint32_t r = grp; r < rows; r += G) {
+          const float4 p = *reinterpret_cast<const float4 *>(px + (size_t)r * Lw);
+          const float4 w = *reinterpret_cast<const float4 *>(pd + (size_t)r * Lw);
+          const float e[4] = {p.x, p.y, p.z, p.w}, f[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float d = e[i] - cm[i];
+            const float yb = fmaf(d, cs[i], cbt[i]);
+            const float dz = relu ? f[i] * (yb > 0.0f ? 1.0f : 0.0f) : f[i];
+            s1[i] += dz; s2[i] = fmaf(dz, d, s2[i]);
+          }
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { colA[grp * Lw + 4 * v + i] = s1[i]; colB[grp * Lw + 4 * v + i] = s2[i]; }
+      }
+    }
+    __syncthreads();
+
+    // ---- columns -> channels of this block, fixed order, double precision.
+    // Level 1: one thread per column folds the row groups (results replace group 0's entries;
+    // every column has seen all `rows` samples).  Moments travel as (n, n*mean, M2 + n*mean^2):
+    // plain sums in f64, which lose nothing that f32 inputs could have carried.
+    const uint32_t Gr = G < rows ? G : rows;
+    for (uint32_t col = tid; col < Lw; col += kSegThreads) {
+      if (DIR == 0) {
+        double t1 = 0.0, t2 = 0.0;
+        for (uint32_t gi = 0; gi < Gr; ++gi) {
+          const double n = (double)((rows - gi + G - 1) / G), m = (double)colA[gi * Lw + col];
+          t1 = fma(n, m, t1); t2 += (double)colB[gi * Lw + col] + n * m * m;
+        }
+        const double mean = rows ? t1 / (double)rows : 0.0;
+        colA[col] = (float)mean; colB[col] = (float)fmax(t2 - t1 * mean, 0.0);
+      } else {
+        double t1 = 0.0, t2 = 0.0;
+        for (uint32_t gi = 0; gi < Gr; ++gi) { t1 += (double)colA[gi * Lw + col]; t2 += (double)colB[gi * Lw + col]; }
+        colA[col] = (float)t1; colB[col] = (float)t2;
+      }
+    }
+    __syncthreads();
+    // Level 2: one warp per channel over its dim0 columns
+    for (uint32_t ci = warp; ci < cw; ci += kSegThreads / 32) {
+      double t1 = 0.0, t2 = 0.0;
+      for (uint32_t p = lane; p < dim0; p += 32) {
+        const double m = (double)colA[ci * dim0 + p], w = (double)colB[ci * dim0 + p];
+        if (DIR == 0) { t1 += m; t2 += w + (double)rows * m * m; } else { t1 += m; t2 += w; }
+      }
+      t1 = warp_sum_all(t1); t2 = warp_sum_all(t2);
+      if (lane == 0) {
+        if (DIR == 0) {
+          const double n = (double)rows * (double)dim0, mean = t1 / (double)dim0;      // equal counts per column
+          part[ci] = make_float4((float)n, (float)mean, (float)fmax(t2 - (double)rows * t1 * mean, 0.0), 0.f);
+        } else {
+          part[ci] = make_float4((float)t1, (float)t2, 0.f, 0.f);
+        }
+      }
+    }
+    cluster.sync();
+
+    // ---- merge the cluster's partials in rank order; every block computes the same coefficients
+    for (uint32_t ci = tid; ci < cw; ci += kSegThreads) {
+      const uint32_t c = c0 + ci;
+      const float gm = a.gamma ? a.gamma[c] : 1.0f;
+      const float bt = (a.gamma && a.beta) ? a.beta[c] : 0.0f;
+      double t0 = 0.0, t1 = 0.0, t2 = 0.0;
+#pragma unroll 4
+      for (uint32_t r = 0; r < g.cluster; ++r) {
+        const float4 p = *cluster.map_shared_rank(part + ci, r);
+        if (DIR == 0) { const double n = (double)p.x, m = (double)p.y; t0 += n; t1 = fma(n, m, t1); t2 += (double)p.z + n * m * m; }
+        else { t1 += (double)p.x; t2 += (double)p.y; }
+      }
+      if (DIR == 0) {
+        const double mean = t1 / t0, m2 = fmax(t2 - t1 * mean, 0.0);
+        const float mf = (float)mean;
+        const float vf = (float)(m2 / t0 + (double)a.epsilon);        // biased, epsilon folded in (batch_norm.cu:160)
+        coef[8 * ci + 0] = mf; coef[8 * ci + 1] = gm * inv_std(vf); coef[8 * ci + 2] = bt;
+        if (rank == 0) {
+          a.mean[c] = mf; a.var[c] = vf;
+          if (a.run_mean) { const float o = a.run_mean[c]; a.run_mean[c] = o + a.avg_rate * (mf - o); }
+          if (a.run_var) { const float o = a.run_var[c]; a.run_var[c] = o + a.avg_rate * (vf - o); }
+        }
+      } else {
+        const float rstd = inv_std(a.var_in[c]);
+        const double rs2 = (double)rstd * t2;                         // sum(dz * xhat)
+        const double A = (double)gm * (double)rstd;
+        const double invM = 1.0 / a.count_total;
+        coef[8 * ci + 3] = (float)(-A * (double)rstd * rs2 * invM);
+        coef[8 * ci + 4] = (float)(-A * t1 * invM);
+        if (rank == 0) {
+          if (a.dbeta) a.dbeta[c] = (float)t1;
+          if (a.dgamma) a.dgamma[c] = (float)rs2;
+        }
+      }
+    }
+    __syncthreads();
+
+    // ---- apply from shared memory, stream the result out
+    if (active) {
+      float cm[4], cs[4], cbt[4], cB[4], cC[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        cm[i] = coef[8 * ch[i] + 0]; cs[i] = coef[8 * ch[i] + 1]; cbt[i] = coef[8 * ch[i] + 2];
+        cB[i] = DIR == 1 ? coef[8 * ch[i] + 3] : 0.f; cC[i] = DIR == 1 ? coef[8 * ch[i] + 4] : 0.f;
+      }
+      const float *px = sx + 4 * (size_t)v, *pd = sdy + 4 * (size_t)v;
+      float *po = a.out + (size_t)n0 * rs + (size_t)c0 * dim0 + 4 * (size_t)v;
+      for (uint32_t r = grp; r < rows; r += G) {
+        const float4 p = *reinterpret_cast<const float4 *>(px + (size_t)r * Lw);
+        const float e[4] = {p.x, p.y, p.z, p.w};
+        float o[4];
+        if (DIR == 0) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) { const float yb = fmaf(e[i] - cm[i], cs[i], cbt[i]); o[i] = relu ? positive_clip(yb) : yb; }
+        } else {
+          const float4 w = *reinterpret_cast<const float4 *>(pd + (size_t)r * Lw);
+          const float f[4] = {w.x, w.y, w.z, w.w};
+          float old[4] = {0.f, 0.f, 0.f, 0.f};
+          if (acc) { const float4 t = *reinterpret_cast<const float4 *>(po + (size_t)r * rs); old[0] = t.x; old[1] = t.y; old[2] = t.z; old[3] = t.w; }
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float d = e[i] - cm[i];
+            const float yb = fmaf(d, cs[i], cbt[i]);
+            const float dz = relu ? f[i] * (yb > 0.0f ? 1.0f : 0.0f) : f[i];
+            const float dx = fmaf(cs[i], dz, fmaf(cB[i], d, cC[i]));
+            o[i] = acc ? old[i] + dx : dx;
+          }
+        }
+        __stcs(reinterpret_cast<float4 *>(po + (size_t)r * rs), make_float4(o[0], o[1], o[2], o[3]));
+      }
+    }
+    __syncthreads();      // this stage, the column arrays and the coefficients may be reused
+  }
+  cluster.sync();         // nobody leaves while a neighbour may still read its partials
+}
+
+// ---- host side -------------------------------------------------------------------------------
+
+// Two ways to overlap copies with arithmetic, chosen by environment for experiments:
+//   stages 1 (default): one unit per cluster and launch, two blocks share an SM;
+//   stages 2: persistent clusters, one block per SM holding two slices (the next unit's copies are
+//   in flight while the current one is worked on).  Measured slower: what limits this kernel is the
+//   chain of short dependent phases per unit, which co-resident blocks overlap better.
+static uint32_t seg_env(const char *name, uint32_t lo, uint32_t hi, uint32_t dflt)
+{
+  const char *e = getenv(name);
+  const long n = e ? strtol(e, nullptr, 10) : 0;
+  return (uint32_t)((e && n >= (long)lo && n <= (long)hi) ? n : dflt);
+}
+static uint32_t seg_stages() { static const uint32_t v = seg_env("ANODE_B200_SEG_STAGES", 1, 2, 1); return v; }
+static uint32_t seg_blocks_per_sm()
+{
+  static const uint32_t v = seg_env("ANODE_B200_SEG_BLOCKS_PER_SM", 1, 4, seg_stages() == 2 ? 1 : 2);
+  return v;
+}
+
+// Geometry for direction `dir`, or false when this kernel does not apply: the shape is not a
+// "segments" shape, or a unit does not fit the shared memory of one cluster.
+static bool seg_geom(uint32_t dim0, uint32_t C, uint32_t N, int dir, SegGeom &g)
+{
+  const uint64_t row_stride = (uint64_t)C * dim0;
+  if (row_stride % 4 != 0 || dim0 >= 512) return false;
+  if (dim0 >= 256 && dim0 % 4 == 0) return false;              // long aligned rows: the tiled kernels' case
+  uint32_t q = 4; if (dim0 % 2 == 0) q = 2; if (dim0 % 4 == 0) q = 1;      // cb*dim0 must be a multiple of 4
+  // the smallest cb that gives runs of at least 512 bytes, within 256 float4 columns and 256 channels
+  uint32_t cb = q;
+  while ((uint64_t)cb * dim0 < 128 && (uint64_t)(cb + q) * dim0 <= 4 * kSegThreads && cb + q <= 256) cb += q;
+  if (cb >= C) cb = C;
+  if ((uint64_t)cb * dim0 > 4 * kSegThreads || (cb * dim0) % 4 != 0) return false;
+  const uint32_t L = cb * dim0, tensors = dir == 1 ? 2 : 1;
+  const uint32_t per_block = (228u * 1024u) / seg_blocks_per_sm() - 1024u;       // what one of k co-resident blocks may use
+  const uint32_t budget = per_block > 227u * 1024u ? 227u * 1024u : per_block;
+  g.cb = cb; g.units = ceil_div_u32(C, cb);
+  g.off_col = 0;
+  g.off_coef = 2 * kSegColFloats * 4;
+  g.off_part = g.off_coef + (uint32_t)align_up_u64((uint64_t)cb * 32, 16);
+  g.off_stage = g.off_part + (uint32_t)align_up_u64((uint64_t)2 * cb * 16, 128);
+  // `stages` stages of `tensors` slices each; a slice is padded to 128 bytes
+  g.stages = seg_stages();
+  if (g.off_stage + (uint64_t)g.stages * tensors * ((uint64_t)L * 4 + 128) > budget) return false;
+  const uint32_t rows_max = (uint32_t)(((budget - g.off_stage) / (g.stages * tensors) - 128) / (L * 4));
+  uint32_t cl = 1;
+  while (cl < kSegMaxCluster && (uint64_t)cl * rows_max < N) cl *= 2;
+  if ((uint64_t)cl * rows_max < N) return false;
+  g.cluster = cl;
+  g.rows = ceil_div_u32(N, cl);
+  const uint32_t slice = (uint32_t)align_up_u64((uint64_t)g.rows * L * 4, 128);
+  g.off_dy = slice;                         // within a stage: x, then dy
+  g.stage_bytes = tensors * slice;
+  g.smem_bytes = g.off_stage + g.stages * g.stage_bytes;
+  return g.smem_bytes <= budget;
+}
+
+bool segres_applies(const FusedArgs &a, int dir, bool aligned)
+{
+  SegGeom g;
+  return aligned && a.mode == MODE_FUSED && a.world <= 1 && seg_geom(a.plan.dim0, a.plan.C, a.plan.N, dir, g);
+}
+
+// Launches the segments kernel for a prepared call.  ANODE_E_LAUNCH when the device refuses the
+// cluster shape (the caller falls back to the plain kernel).
+int launch_segres(FusedArgs &a, int dir, cudaStream_t stream)
+{
+  SegGeom g;
+  if (!seg_geom(a.plan.dim0, a.plan.C, a.plan.N, dir, g)) return ANODE_E_LAUNCH;
+  auto kernel = dir == 0 ? bn_segres_kernel<0> : bn_segres_kernel<1>;
+  static std::mutex mu;
+  static std::map<std::pair<const void *, uint64_t>, int> fit_cache;     // (kernel, smem | cluster) -> clusters resident at once
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(g.units * g.cluster);
+  cfg.blockDim = dim3(kSegThreads);
+  cfg.dynamicSmemBytes = g.smem_bytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = g.cluster; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr; cfg.numAttrs = 1;
+  int fit = 0;
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    int dev = 0;
+    (void)cudaGetDevice(&dev);
+    const auto key = std::make_pair((const void *)kernel, ((uint64_t)g.smem_bytes << 16) | ((uint64_t)dev << 8) | g.cluster);
+    auto it = fit_cache.find(key);
+    if (it == fit_cache.end()) {
+      int clusters = 0;
+      bool ok = cudaFuncSetAttribute((const void *)kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(227 * 1024)) == cudaSuccess;
+      if (ok && g.cluster > 8)
+        ok = cudaFuncSetAttribute((const void *)kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess;
+      if (ok) ok = cudaOccupancyMaxActiveClusters(&clusters, (const void *)kernel, &cfg) == cudaSuccess && clusters > 0;
+      if (!ok) { (void)cudaGetLastError(); clusters = 0; }
+      it = fit_cache.emplace(key, clusters).first;
+    }
+    fit = it->second;
+  }
+  if (getenv("ANODE_B200_SEG_DEBUG"))
+    fprintf(stderr, "segres dir=%d cb=%u cluster=%u rows=%u units=%u smem=%u resident clusters=%d\n", dir, g.cb, g.cluster,
+            g.rows, g.units, g.smem_bytes, fit);
+  if (fit <= 0) return ANODE_E_LAUNCH;
+  // two stages: as many clusters as are resident at once walk the units; one stage: a cluster per unit
+  const uint32_t clusters = (g.stages == 2 && (uint32_t)fit < g.units) ? (uint32_t)fit : g.units;
+  cfg.gridDim = dim3(clusters * g.cluster);
+  if (cudaLaunchKernelEx(&cfg, kernel, a, g) != cudaSuccess) { (void)cudaGetLastError(); return ANODE_E_LAUNCH; }
+  return ANODE_OK;
+}
+
+}  // namespace anode_b200
+
+// ---- diagnostics: geometry of the cluster kernel for a shape (no GPU needed) ------------------
+// out: applies, cb, cluster, rows per block, units, shared memory bytes
+extern "C" int anode_gpu_batch_norm_segres_geometry(uint32_t dim0, uint32_t dim1, uint32_t dim2, int dir, uint32_t *out)
+{
+  using namespace anode_b200;
+  if (!out || check_dims(dim0, dim1, dim2)) return ANODE_E_DIMS;
+  SegGeom g{};
+  const bool ok = seg_geom(dim0, dim1, dim2, dir, g);
+  out[0] = ok ? 1u : 0u; out[1] = g.cb; out[2] = g.cluster; out[3] = g.rows; out[4] = g.units; out[5] = g.smem_bytes;
+  return ANODE_OK;
+}

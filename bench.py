@@ -376,8 +376,18 @@ def main():
                 "peak_kind": peak_kind, "traffic": None}
 
     w = WORKLOADS[args.workload]
-    kernel_name = "bn_ring_kernel<%s> (fused reduce+apply)" if main_res["launches_per_step"] == 2 else \
-        "reduce kernel + all-gather + merge kernel + apply kernel (%s)"
+    def kernel_name(direction):
+        if main_res["launches_per_step"] != 2:
+            return "reduce kernel + all-gather + merge kernel + apply kernel (%s)" % direction
+        from anode_b200 import _lib
+        shp = local_shape(w, rank, world)
+        d0 = 1
+        for v in shp[2:]:
+            d0 *= int(v)
+        c, n = int(shp[1]), int(shp[0])
+        kind = _lib.load().anode_gpu_batch_norm_fused_kernel_kind(d0, c, n, 0 if direction == "fwd" else 1)
+        return {1: "bn_ring_kernel<%s> (fused reduce+apply, tiled)", 2: "bn_segres_kernel<%s> (fused reduce+apply, clusters)",
+                0: "bn_pipeline_kernel<%s> (fused reduce+apply, plain)"}.get(kind, "?%s") % direction
     line = {
         "metric": "bn_relu_fwd_bwd_elements_per_s", "value": main_res["value"], "unit": "elements/s",
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": main_res["ms_per_step"],
@@ -389,8 +399,8 @@ def main():
                    "exchange": "none" if world == 1 else ("in-kernel peer stores" if main_res["launches_per_step"] == 2 else "nccl all-gather")},
         "per_gpu_value": main_res["value"] / world,
         "fwd_ms": main_res["fwd_ms"], "bwd_ms": main_res["bwd_ms"],
-        "roofline": dict(roof(BYTES_BWD, main_res["bwd_ms"]), kernel=kernel_name % "bwd"),
-        "roofline_fwd": dict(roof(BYTES_FWD, main_res["fwd_ms"]), kernel=kernel_name % "fwd"),
+        "roofline": dict(roof(BYTES_BWD, main_res["bwd_ms"]), kernel=kernel_name("bwd")),
+        "roofline_fwd": dict(roof(BYTES_FWD, main_res["fwd_ms"]), kernel=kernel_name("fwd")),
         "roofline_step": roof(BYTES_FWD + BYTES_BWD, main_res["ms_per_step"]),
         "clocks": main_res["clocks"],
         "gpu_launches": main_res["launches_per_step"] * args.steps,
