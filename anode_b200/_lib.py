@@ -57,11 +57,13 @@ SIGNATURES = {
     "anode_gpu_batch_norm_host_step_blocks": (u32, _D + [u32]),
     "anode_gpu_batch_norm_relu_fused_step_host_3d1_packed_f32":
         (c_int, _D + [f32, f32, c_int] + [vp] * 12 + [vp, size_t, u32] + _T),
+    "anode_gpu_batch_norm_act_infer_3d1_packed_f32": (c_int, _D + [f32] + [vp] * 6 + _T),
     "anode_gpu_online_average_f32": (c_int, [u32, f32, vp, vp] + _T),
     "anode_gpu_sync_unique_id_bytes": (size_t, []),
     "anode_gpu_sync_get_unique_id": (c_int, [vp]),
     "anode_gpu_sync_comm_create": (c_int, [vp, c_int, c_int, ctypes.POINTER(vp)]),
     "anode_gpu_sync_comm_destroy": (c_int, [vp]),
+    "anode_gpu_sync_allreduce_sum_f32": (c_int, [vp, vp, size_t, vp]),
     "anode_gpu_sync_exchange_bytes": (size_t, [u32, c_int]),
     "anode_gpu_sync_comm_attach_exchange": (c_int, [vp, ctypes.POINTER(vp), u32]),
     "anode_gpu_sync_batch_norm_workspace_bytes": (size_t, _D + [c_int]),

@@ -11,7 +11,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libanode_routines_gpu.so")
-SOURCES = ["bn_fused.cu", "bn_legacy.cu", "bn_sync.cu", "bn_static.cu", "bn_hoststep.cu", "bn_segres.cu"]
+SOURCES = ["bn_fused.cu", "bn_legacy.cu", "bn_sync.cu", "bn_static.cu", "bn_hoststep.cu", "bn_segres.cu", "bn_infer.cu"]
 HEADERS = ["bn_plan.h", "bn_device.cuh", "bn_fused.cuh", "bn_ring.cuh", "bn_host.h", "bn_sync.h",
            os.path.join("..", "..", "include", "anode_routines_gpu.h")]
 

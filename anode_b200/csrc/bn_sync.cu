@@ -26,6 +26,7 @@ struct NcclApi {
   ncclResult_t (*CommInitRank)(ncclComm_t *, int, ncclUniqueId, int);
   ncclResult_t (*CommDestroy)(ncclComm_t);
   ncclResult_t (*AllGather)(const void *, void *, size_t, ncclDataType_t, ncclComm_t, cudaStream_t);
+  ncclResult_t (*AllReduce)(const void *, void *, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t, cudaStream_t);
   const char *(*GetErrorString)(ncclResult_t);
   bool ok;
 };
@@ -42,8 +43,9 @@ static const NcclApi &nccl()
     a.CommInitRank = (decltype(a.CommInitRank))dlsym(h, "ncclCommInitRank");
     a.CommDestroy = (decltype(a.CommDestroy))dlsym(h, "ncclCommDestroy");
     a.AllGather = (decltype(a.AllGather))dlsym(h, "ncclAllGather");
+    a.AllReduce = (decltype(a.AllReduce))dlsym(h, "ncclAllReduce");
     a.GetErrorString = (decltype(a.GetErrorString))dlsym(h, "ncclGetErrorString");
-    a.ok = a.GetUniqueId && a.CommInitRank && a.CommDestroy && a.AllGather;
+    a.ok = a.GetUniqueId && a.CommInitRank && a.CommDestroy && a.AllGather && a.AllReduce;
     return a;
   }();
   return api;
@@ -169,6 +171,20 @@ extern "C" int anode_gpu_sync_comm_attach_exchange(struct AnodeSyncComm *comm, v
   }
   comm->xchg_channels = max_channels;
   comm->epoch = 0;
+  return ANODE_OK;
+}
+
+// Sum of a device buffer over the ranks of `comm`, in place, on `stream`: what SumSpmdOp does for
+// gradients through a host-staged MPI_Allreduce (src/ops_gpu.rs:538-545, src/proc_mpi.rs:138-148),
+// here over NVLink without leaving the device.
+extern "C" int anode_gpu_sync_allreduce_sum_f32(struct AnodeSyncComm *comm, float *buf, size_t len, struct CUstream_st *stream)
+{
+  if (!comm) return ANODE_E_COMM;
+  if (!buf && len) return ANODE_E_NULL;
+  if (len == 0 || comm->world == 1) return ANODE_OK;
+  const NcclApi &api = nccl();
+  if (!api.ok || !comm->nccl) return ANODE_E_COMM;
+  if (api.AllReduce(buf, buf, len, ncclFloat, ncclSum, comm->nccl, stream) != ncclSuccess) return ANODE_E_COMM;
   return ANODE_OK;
 }
 

@@ -362,6 +362,21 @@ class BatchNormalize2dBwdFusedOp:
 BatchNormalize3dFusedOp, BatchNormalize3dBwdFusedOp = BatchNormalize2dFusedOp, BatchNormalize2dBwdFusedOp
 
 
+class BatchNormalize2dActInferOp:
+    """Inference: batch-norm with given (running) statistics and the activation after it in one pass.
+    neg_slope 0 = ReLU (positive_clip), 1 = none, c = leaky ReLU (flat_map.cu:44-52)."""
+    @staticmethod
+    def apply(axes, x, mean, var, y, gamma=None, beta=None, neg_slope=0.0, cfg=None, stream=None):
+        d0, c, n = dims_of(x, axes)
+        check(_lib.load().anode_gpu_batch_norm_act_infer_3d1_packed_f32(
+            d0, c, n, ctypes.c_float(neg_slope), _p(x), _p(mean), _p(var), _p(gamma), _p(beta), _p(y),
+            _cfg(cfg), _stream(stream)), "anode_gpu_batch_norm_act_infer_3d1_packed_f32")
+        return y
+
+
+BatchNormalize3dActInferOp = BatchNormalize2dActInferOp
+
+
 class FusedBatchNormRelu:
     """A batch-norm + ReLU layer that keeps its own buffers (statistics, running averages,
     workspace), so that a training loop makes two calls per step: forward(x) and backward(dy)."""
@@ -379,6 +394,7 @@ class FusedBatchNormRelu:
         self.dbeta = torch.zeros(channels, device=dev) if affine else None
         self._ws = None
         self._staging = None
+        self._dev = None
         self._x = None
 
     launches_per_step = 2      # one forward kernel, one backward kernel
@@ -432,6 +448,13 @@ class FusedBatchNormRelu:
             ctypes.c_void_p(self._staging.data_ptr()), _stream(None), ctypes.byref(out)), "status")
         return int(out.value)
 
+    def infer(self, x, out=None):
+        """Evaluation mode: normalize with the running averages, then the activation."""
+        axes = list(range(x.dim() - 2))
+        y = out if out is not None else torch.empty_like(x)
+        return BatchNormalize2dActInferOp.apply(axes, x, self.avg_mean, self.avg_var, y, self.gamma, self.beta,
+                                                0.0 if self.relu else 1.0)
+
     def forward(self, x, out=None):
         axes = list(range(x.dim() - 2))
         y = out if out is not None else torch.empty_like(x)
@@ -475,9 +498,24 @@ class SyncBatchNormRelu(FusedBatchNormRelu):
         merge kernel and apply kernel (plus one NCCL all-gather)."""
         return 2 if getattr(self.comm, "_exchange", None) is not None else 6
 
-    def step_from_host(self, *args, **kw):
-        raise NotImplementedError("the host-buffer step cuts the layer by channels on one GPU; "
-                                  "shard the host batch and call forward/backward instead")
+    def step_from_host(self, hx, hdy, hy, hdx, chunk_channels=0):
+        """This rank's shard in (page-locked) host memory: whole-shard copies around the two
+        synchronized kernels, all on the current stream (the single-GPU pipeline over channel blocks
+        is not used here: every block would be a collective of its own).  Returns 1."""
+        dev = self.mean.device
+        if self._dev is None or self._dev[0].shape != hx.shape:
+            self._dev = tuple(torch.empty(hx.shape, dtype=torch.float32, device=dev) for _ in range(3))
+        x, dy, y = self._dev
+        x.copy_(hx, non_blocking=True)
+        dy.copy_(hdy, non_blocking=True)
+        self.forward(x, out=y)
+        self.backward(dy, out=dy)              # dx over dy
+        hy.copy_(y, non_blocking=True)
+        hdx.copy_(dy, non_blocking=True)
+        return 1
+
+    def host_step_status(self):
+        return self.status()
 
     def __init__(self, channels, comm=None, global_count=None, exchange=True, **kw):
         super().__init__(channels, **kw)

@@ -98,6 +98,17 @@ class SyncComm:
         self._exchange = (buf, hdl)          # keep the mapping alive
         return self
 
+    def allreduce_sum(self, buf):
+        """In-place sum of a float32 CUDA tensor over the ranks, on the current stream: the
+        device-side counterpart of SumSpmdOp's host-staged MPI_Allreduce (src/ops_gpu.rs:538-545)."""
+        import torch
+        if not (buf.is_cuda and buf.dtype == torch.float32 and buf.is_contiguous()):
+            raise ValueError("expected a contiguous float32 CUDA tensor")
+        stream = ctypes.c_void_p(torch.cuda.current_stream(buf.device).cuda_stream)
+        check(_lib.load().anode_gpu_sync_allreduce_sum_f32(self.handle, ctypes.c_void_p(buf.data_ptr()),
+                                                           buf.numel(), stream), "anode_gpu_sync_allreduce_sum_f32")
+        return buf
+
     def destroy(self):
         if self.handle:
             _lib.load().anode_gpu_sync_comm_destroy(self.handle)

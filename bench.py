@@ -292,8 +292,28 @@ def bench_workload(ops, name, rank, world, steps, warmup, dist, device, sample_c
     res = {"ms_per_step": ms, "fwd_ms": fwd, "bwd_ms": bwd, "elements_local": n_local, "elements_global": n_global,
            "value": n_global / (ms * 1e-3), "clocks": clocks, "launches_per_step": layer.launches_per_step}
     if with_e2e:
+        res["infer"] = bench_infer(layer, x, y, steps, warmup)
         res["e2e"] = bench_e2e(ops, layer, x, dy, y, dx, dist, device, min(steps, 3))
     return res
+
+
+def bench_infer(layer, x, y, steps, warmup):
+    """Evaluation-mode pass (running statistics + ReLU in one kernel): 8 bytes per element."""
+    import torch
+    for _ in range(max(warmup, 3)):
+        layer.infer(x, out=y)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        layer.infer(x, out=y)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    peak, kind = hbm_peak()
+    gbs = 8.0 * x.numel() / (ms * 1e-3) / 1e9
+    return {"kernel": "bn_infer_kernel", "ms": ms, "elements_per_s": x.numel() / (ms * 1e-3), "achieved_gbs": gbs,
+            "frac_of_hbm_peak": gbs / peak, "peak_kind": kind}
 
 
 def bench_e2e(ops, layer, x, dy, y, dx, dist, device, steps):
@@ -303,7 +323,8 @@ def bench_e2e(ops, layer, x, dy, y, dx, dist, device, steps):
     hdy = torch.empty(x.shape, dtype=torch.float32, pin_memory=True); hdy.copy_(dy)
     hy = torch.empty(x.shape, dtype=torch.float32, pin_memory=True)
     hdx = torch.empty(x.shape, dtype=torch.float32, pin_memory=True)
-    blocks = layer.step_from_host(hx, hdy, hy, hdx)      # warm-up
+    chunk = int(os.environ.get("ANODE_BENCH_E2E_CHUNK", "0"))      # channels per block; 0: the library's choice
+    blocks = layer.step_from_host(hx, hdy, hy, hdx, chunk)      # warm-up
     torch.cuda.synchronize()
     if dist is not None:
         dist.barrier()
@@ -311,7 +332,7 @@ def bench_e2e(ops, layer, x, dy, y, dx, dist, device, steps):
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(steps):
-        layer.step_from_host(hx, hdy, hy, hdx)
+        layer.step_from_host(hx, hdy, hy, hdx, chunk)
     e1.record()
     torch.cuda.synchronize()
     if dist is not None:
@@ -325,8 +346,9 @@ def bench_e2e(ops, layer, x, dy, y, dx, dist, device, steps):
     return {"value": x.numel() * world / (ms * 1e-3), "unit": "elements/s", "ms_per_step": ms, "steps": steps,
             "h2d_bytes_per_step": 2 * nbytes, "d2h_bytes_per_step": 2 * nbytes,
             "channel_blocks": blocks, "gpu_launches_per_step": 2 * blocks,
-            "how": "one C-ABI call per step on pinned host tensors; channel blocks, copies in both directions "
-                   "overlapped with the kernels"}
+            "how": ("one C-ABI call per step on pinned host tensors; channel blocks, copies in both directions "
+                    "overlapped with the kernels") if world == 1 else
+                   "per rank: shard copied in, two synchronized kernels, shard copied out, on one stream"}
 
 
 def main():
@@ -407,6 +429,8 @@ def main():
     }
     if "e2e" in main_res:
         line["e2e"] = main_res["e2e"]
+    if "infer" in main_res:
+        line["infer"] = main_res["infer"]
     tr = TRAFFIC.get(args.workload if world == 1 else "%s@%d" % (args.workload, world), {})
     for key, rk in (("bwd", "roofline"), ("fwd", "roofline_fwd")):
         if key in tr:

@@ -271,6 +271,18 @@ int anode_gpu_batch_norm_relu_fused_step_host_3d1_packed_f32(
     void *staging, size_t staging_bytes, uint32_t chunk_channels,
     const struct KernelConfig *cfg, struct CUstream_st *stream);
 
+/* Batch-norm with given statistics fused with the activation that follows it (one pass, 8 bytes
+ * per element): the inference branch of batch_normalize_2d/3d (src/ops.rs:1010-1011, the switch on
+ * `online` selects the running averages; anode_gpu_batch_norm_3d1_packed_f32 computes it without
+ * activation) followed by positive_clip (flat_map.cu:172-179) or leaky ReLU (flat_map.cu:44-52):
+ *   y = act(gamma[c]*(x-mean[c])*var[c]^-1/2 + beta[c]),  act(t) = t*(t > 0 ? 1 : neg_slope)
+ * neg_slope = 0: ReLU, 1: no activation, c: leaky ReLU with constant c.  var is biased variance +
+ * epsilon, as anode stores it.  gamma/beta may be NULL.  y may be x. */
+int anode_gpu_batch_norm_act_infer_3d1_packed_f32(
+    uint32_t dim0, uint32_t dim1, uint32_t dim2, float neg_slope,
+    const float *x, const float *mean, const float *var, const float *gamma, const float *beta,
+    float *y, const struct KernelConfig *cfg, struct CUstream_st *stream);
+
 /* Running-statistic update on its own (OnlineAverageOp, src/ops_gpu.rs:6034-6077; rule
  * pinned by tests/test_gpu.rs:561-593):  y[i] += rate*(x[i] - y[i]). */
 int anode_gpu_online_average_f32(
@@ -296,6 +308,11 @@ size_t anode_gpu_sync_unique_id_bytes(void);
 int anode_gpu_sync_get_unique_id(void *out);
 int anode_gpu_sync_comm_create(const void *unique_id, int rank, int world, struct AnodeSyncComm **out);
 int anode_gpu_sync_comm_destroy(struct AnodeSyncComm *comm);
+
+/* In-place sum of buf[0..len) over the ranks (ncclAllReduce on `stream`): the device-side form of
+ * SumSpmdOp's host-staged MPI_Allreduce of gradients (src/ops_gpu.rs:538-545,
+ * src/proc_mpi.rs:138-148), reusing the communicator of the synchronized batch-norm. */
+int anode_gpu_sync_allreduce_sum_f32(struct AnodeSyncComm *comm, float *buf, size_t len, struct CUstream_st *stream);
 
 /* Optional: exchange inside the kernels instead of an NCCL all-gather between them.
  * Every rank allocates a buffer of anode_gpu_sync_exchange_bytes(max_channels, world) bytes that

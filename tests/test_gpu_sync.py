@@ -34,12 +34,18 @@ def _worker(rank, world, port, shape, axis, out_dir, dist_kind, exchange):
     layer = ops.SyncBatchNormRelu(shape[1], epsilon=1e-5, avg_rate=0.1, exchange=exchange)
     assert layer.launches_per_step == (2 if (exchange and world > 1) else 6)
     layer.gamma.copy_(torch.from_numpy(d["gamma"])); layer.beta.copy_(torch.from_numpy(d["beta"]))
-    for _ in range(2):                      # twice: the workspace must come back clean
+    # twice on one workspace, other data the first time: nothing of a step may reach the next one
+    for xs, dys in ((x * 2.0 + 1.0, dy * 0.5), (x, dy)):
         layer.avg_mean.zero_(); layer.avg_var.fill_(1.0)
-        y = layer.forward(x)
-        dx = layer.backward(dy)
+        y = layer.forward(xs)
+        dx = layer.backward(dys)
     torch.cuda.synchronize()
     assert layer.status() == 0
+    # the gradient all-reduce that shares the communicator (SumSpmdOp's role)
+    grad = torch.full((1000,), float(rank + 1), device="cuda")
+    layer.comm.allreduce_sum(grad)
+    torch.cuda.synchronize()
+    assert (grad == world * (world + 1) / 2).all()
     np.savez(os.path.join(out_dir, "r%d.npz" % rank), y=y.cpu().numpy(), dx=dx.cpu().numpy(),
              mean=layer.mean.cpu().numpy(), var=layer.var.cpu().numpy(), run_mean=layer.avg_mean.cpu().numpy(),
              run_var=layer.avg_var.cpu().numpy(), dgamma=layer.dgamma.cpu().numpy(), dbeta=layer.dbeta.cpu().numpy())
