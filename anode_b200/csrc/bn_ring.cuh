@@ -12,11 +12,15 @@
 //                    results with 128-bit streaming stores, and hand partials to the delivery
 //                    warp through a shared-memory mailbox.  In regime R every warp works on its
 //                    own share of a tile and never synchronises with the other warps.
-//   delivery warp    moves partials from the mailbox to the workspace, counts them per unit and,
-//                    for the partial that completes a unit, merges all of the unit's partials
-//                    in double precision and publishes one tagged 64-bit record per channel.
-//   coefficient warp polls the records of the units of upcoming apply visits (a record is its
-//                    own ready flag) and stages the visit's coefficients in a second mailbox.
+//   delivery warp    merges the consumer warps' partials of a tile and stores them as ONE tagged
+//                    8-byte word per tile in the workspace (no counter, no fence, no atomic).
+//   coefficient warp polls, for each upcoming apply visit, the partial words of the visit's
+//                    channel until none is zero, merges them in a fixed order in double
+//                    precision (every block obtains bit-identical coefficients; with several
+//                    GPUs the owner block exchanges per-GPU records with the peers here) and
+//                    stages the visit's coefficients in a second mailbox.
+//                    (The split modes used with the NCCL exchange still count partials per unit
+//                    and publish per-channel records.)
 //
 // Every wait is bounded: a wait that runs out sets a status bit, raises the block's abort flag
 // and all three roles drain and leave.
