@@ -295,7 +295,7 @@ int prepare_fwd(FusedArgs &a, uint32_t dim0, uint32_t dim1, uint32_t dim2, float
   a.x = x; a.gamma = gamma; a.beta = beta; a.out = y;
   a.mean = mean; a.var = var; a.run_mean = run_mean; a.run_var = run_var;
   a.ws = static_cast<unsigned char *>(ws);
-  a.epsilon = epsilon; a.avg_rate = avg_rate; a.relu = relu ? 1u : 0u;
+  a.epsilon = epsilon; a.avg_rate = avg_rate; a.relu = relu ? 1u : 0u; a.neg_slope = relu ? 0.0f : 1.0f;
   a.mode = MODE_FUSED;
   a.count_total = (double)dim0 * (double)dim2;
   return ANODE_OK;
@@ -319,7 +319,7 @@ int prepare_bwd(FusedArgs &a, uint32_t dim0, uint32_t dim1, uint32_t dim2, int r
   a.x = x; a.dy = dy; a.gamma = gamma; a.beta = beta; a.mean_in = mean; a.var_in = var;
   a.out = dx; a.dgamma = dgamma; a.dbeta = dbeta;
   a.ws = static_cast<unsigned char *>(ws) + part;              // the backward part
-  a.relu = relu ? 1u : 0u; a.accumulate = accumulate ? 1u : 0u;
+  a.relu = relu ? 1u : 0u; a.neg_slope = relu ? 0.0f : 1.0f; a.accumulate = accumulate ? 1u : 0u;
   a.mode = MODE_FUSED;
   a.count_total = (double)dim0 * (double)dim2;
   return ANODE_OK;
@@ -387,6 +387,38 @@ extern "C" int anode_gpu_batch_norm_relu_fused_bwd_3d1_packed_f32(
   const int rc = prepare_bwd(a, dim0, dim1, dim2, relu, accumulate, dy, x, mean, var, gamma, beta, dx,
                              dgamma, dbeta, workspace, workspace_bytes);
   if (rc) return rc;
+  return launch_best(a, 1, aligned16(x) && aligned16(dy) && aligned16(dx), stream);
+}
+
+// The two calls above with a general activation t*(t > 0 ? 1 : neg_slope) instead of the ReLU switch.
+extern "C" int anode_gpu_batch_norm_act_fused_fwd_3d1_packed_f32(
+    uint32_t dim0, uint32_t dim1, uint32_t dim2, float epsilon, float avg_rate, float neg_slope,
+    const float *x, const float *gamma, const float *beta,
+    float *y, float *mean, float *var, float *run_mean, float *run_var,
+    void *workspace, size_t workspace_bytes, const struct KernelConfig *cfg, struct CUstream_st *stream)
+{
+  (void)cfg;
+  FusedArgs a;
+  const int rc = prepare_fwd(a, dim0, dim1, dim2, epsilon, avg_rate, 1, x, gamma, beta, y, mean, var,
+                             run_mean, run_var, workspace, workspace_bytes);
+  if (rc) return rc;
+  if (workspace_bytes < anode_gpu_batch_norm_fused_workspace_bytes(dim0, dim1, dim2)) return ANODE_E_WORKSPACE;
+  a.neg_slope = neg_slope;
+  return launch_best(a, 0, aligned16(x) && aligned16(y), stream);
+}
+
+extern "C" int anode_gpu_batch_norm_act_fused_bwd_3d1_packed_f32(
+    uint32_t dim0, uint32_t dim1, uint32_t dim2, float neg_slope, int accumulate,
+    const float *dy, const float *x, const float *mean, const float *var,
+    const float *gamma, const float *beta, float *dx, float *dgamma, float *dbeta,
+    void *workspace, size_t workspace_bytes, const struct KernelConfig *cfg, struct CUstream_st *stream)
+{
+  (void)cfg;
+  FusedArgs a;
+  const int rc = prepare_bwd(a, dim0, dim1, dim2, 1, accumulate, dy, x, mean, var, gamma, beta, dx,
+                             dgamma, dbeta, workspace, workspace_bytes);
+  if (rc) return rc;
+  a.neg_slope = neg_slope;
   return launch_best(a, 1, aligned16(x) && aligned16(dy) && aligned16(dx), stream);
 }
 

@@ -40,6 +40,7 @@ struct FusedArgs {
   uint32_t *status;        // the workspace's status word (first word of the caller's buffer)
   float epsilon, avg_rate;
   uint32_t relu, accumulate, mode;
+  float neg_slope;         // activation t*(t > 0 ? 1 : neg_slope): 0 = ReLU, 1 = none, c = leaky ReLU (flat_map.cu:44-52)
   uint32_t use_rec;        // publish tagged records (the warp-specialised kernel reads them)
   double count_total;      // elements per channel over all participating GPUs
   // cross-GPU exchange inside the kernel (world > 1): xchg[r] is rank r's exchange buffer as
@@ -281,7 +282,7 @@ __device__ __forceinline__ void apply_fwd_R(const FusedArgs &a, const TileRange 
   const uint32_t mul = a.plan.div_mul;
   const float4 cf = __ldcg(ws_f4(a, a.plan.off_coef) + 2 * (size_t)tr.c0);
   const float mean = cf.x, scale = cf.y, beta = cf.z;
-  const bool relu = a.relu != 0;
+  const float slope = a.neg_slope;      // activation: t * (t > 0 ? 1 : slope)
   const uint64_t drop = policy_drop();
   for (uint32_t j0 = tid; j0 < nvec; j0 += kThreads * kUnroll) {
     Pack<VEC> v[kUnroll];
@@ -299,7 +300,7 @@ __device__ __forceinline__ void apply_fwd_R(const FusedArgs &a, const TileRange 
 #pragma unroll
         for (int i = 0; i < VEC; ++i) {
           const float yb = fmaf(v[u].v[i] - mean, scale, beta);
-          v[u].v[i] = relu ? positive_clip(yb) : yb;
+          v[u].v[i] = yb * (yb > 0.0f ? 1.0f : slope);
         }
         v[u].store(a.out + off[u], drop);
       }
@@ -319,7 +320,7 @@ __device__ __forceinline__ void reduce_bwd_R(const FusedArgs &a, const TileRange
   const float g = a.gamma ? a.gamma[c] : 1.0f;
   const float beta = (a.gamma && a.beta) ? a.beta[c] : 0.0f;
   const float scale = g * inv_std(a.var_in[c]);
-  const bool relu = a.relu != 0;
+  const float slope = a.neg_slope;      // activation: t * (t > 0 ? 1 : slope)
   const uint64_t keep = policy_keep();
   float s1 = 0.f, s2 = 0.f;
   for (uint32_t j0 = tid; j0 < nvec; j0 += kThreads * kUnroll) {
@@ -343,7 +344,7 @@ __device__ __forceinline__ void reduce_bwd_R(const FusedArgs &a, const TileRange
         const float d = vx[u].v[i] - mean;
         const float yb = fmaf(d, scale, beta);
         // dz = dy * (float)(y > 0)  (routines_gpu/flat_map.cu:191-192)
-        const float dz = relu ? vd[u].v[i] * (yb > 0.0f ? 1.0f : 0.0f) : vd[u].v[i];
+        const float dz = vd[u].v[i] * (yb > 0.0f ? 1.0f : slope);
         s1 += dz; s2 = fmaf(dz, d, s2);
       }
   }
@@ -361,7 +362,8 @@ __device__ __forceinline__ void apply_bwd_R(const FusedArgs &a, const TileRange 
   const float4 c0 = __ldcg(ws_f4(a, a.plan.off_coef) + 2 * (size_t)tr.c0);
   const float4 c1 = __ldcg(ws_f4(a, a.plan.off_coef) + 2 * (size_t)tr.c0 + 1);
   const float mean = c0.x, scale = c0.y, beta = c0.z, cB = c1.x, cC = c1.y;
-  const bool relu = a.relu != 0, acc = a.accumulate != 0;
+  const float slope = a.neg_slope;      // activation: t * (t > 0 ? 1 : slope)
+  const bool acc = a.accumulate != 0;
   const uint64_t drop = policy_drop();
   for (uint32_t j0 = tid; j0 < nvec; j0 += kThreads * kUnroll) {
     Pack<VEC> vx[kUnroll], vd[kUnroll];
@@ -382,7 +384,7 @@ __device__ __forceinline__ void apply_bwd_R(const FusedArgs &a, const TileRange 
         for (int i = 0; i < VEC; ++i) {
           const float d = vx[u].v[i] - mean;
           const float yb = fmaf(d, scale, beta);
-          const float dz = relu ? vd[u].v[i] * (yb > 0.0f ? 1.0f : 0.0f) : vd[u].v[i];
+          const float dz = vd[u].v[i] * (yb > 0.0f ? 1.0f : slope);
           const float dx = fmaf(scale, dz, fmaf(cB, d, cC));
           o.v[i] = acc ? o.v[i] + dx : dx;
         }
@@ -502,7 +504,7 @@ __device__ __forceinline__ void reduce_bwd_S(const FusedArgs &a, const TileRange
       s1[k][i] = 0.f; s2[k][i] = 0.f;
     }
   }
-  const bool relu = a.relu != 0;
+  const float slope = a.neg_slope;      // activation: t * (t > 0 ? 1 : slope)
   const float *bx = a.x + tr.base, *bd = a.dy + tr.base;
   constexpr int U = 2;
   for (uint32_t r0 = 0; r0 < tr.rows; r0 += U) {
@@ -528,7 +530,7 @@ __device__ __forceinline__ void reduce_bwd_S(const FusedArgs &a, const TileRange
         for (int i = 0; i < 4; ++i) {
           const float d = px[u][k].v[i] - cm[k][i];
           const float yb = fmaf(d, cs[k][i], cb[k][i]);
-          const float dz = relu ? pd[u][k].v[i] * (yb > 0.0f ? 1.0f : 0.0f) : pd[u][k].v[i];
+          const float dz = pd[u][k].v[i] * (yb > 0.0f ? 1.0f : slope);
           s1[k][i] += dz; s2[k][i] = fmaf(dz, d, s2[k][i]);
         }
   }
@@ -568,7 +570,8 @@ __device__ __forceinline__ void apply_S(const FusedArgs &a, const TileRange &tr,
       if (DIR == 1) { cB[k][i] = ss.coef[ci * 5 + 3]; cC[k][i] = ss.coef[ci * 5 + 4]; }
     }
   }
-  const bool relu = a.relu != 0, acc = a.accumulate != 0;
+  const float slope = a.neg_slope;      // activation: t * (t > 0 ? 1 : slope)
+  const bool acc = a.accumulate != 0;
   const float *bx = a.x + tr.base;
   float *bo = a.out + tr.base;
   constexpr int U = 2;
@@ -599,9 +602,9 @@ __device__ __forceinline__ void apply_S(const FusedArgs &a, const TileRange &tr,
             const float d = px[u][k].v[i] - cm[k][i];
             const float yb = fmaf(d, cs[k][i], cb[k][i]);
             if (DIR == 0) {
-              o.v[i] = relu ? positive_clip(yb) : yb;
+              o.v[i] = yb * (yb > 0.0f ? 1.0f : slope);
             } else {
-              const float dz = relu ? pd[u][k].v[i] * (yb > 0.0f ? 1.0f : 0.0f) : pd[u][k].v[i];
+              const float dz = pd[u][k].v[i] * (yb > 0.0f ? 1.0f : slope);
               const float dx = fmaf(cs[k][i], dz, fmaf(cB[k][i], d, cC[k][i]));
               o.v[i] = acc ? o.v[i] + dx : dx;
             }

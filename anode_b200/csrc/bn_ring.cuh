@@ -351,7 +351,7 @@ __device__ __forceinline__ void warp_reduce_R(const FusedArgs &a, const RingGeom
     uint32_t ad = ax + g.slot_floats * 4;
     const float4 cf = slot_side<1>(sm, g, slot)[0];
     const float mean = cf.x, scale = cf.y, beta = cf.z;
-    const bool relu = a.relu != 0;
+    const float slope = a.neg_slope;      // activation: t * (t > 0 ? 1 : slope)
     float s1 = 0.f, s2 = 0.f, t1 = 0.f, t2 = 0.f;
     uint32_t i = 0;
     for (; i + 2 <= cnt; i += 2, ax += 2 * kVecStride, ad += 2 * kVecStride) {
@@ -361,8 +361,8 @@ __device__ __forceinline__ void warp_reduce_R(const FusedArgs &a, const RingGeom
         const float d0 = x0.v[e] - mean, d1 = x1.v[e] - mean;
         const float y0 = fmaf(d0, scale, beta), y1 = fmaf(d1, scale, beta);
         // dz = dy * (float)(y > 0)  (routines_gpu/flat_map.cu:191-192)
-        const float z0 = relu ? g0.v[e] * (y0 > 0.0f ? 1.0f : 0.0f) : g0.v[e];
-        const float z1 = relu ? g1.v[e] * (y1 > 0.0f ? 1.0f : 0.0f) : g1.v[e];
+        const float z0 = g0.v[e] * (y0 > 0.0f ? 1.0f : slope);
+        const float z1 = g1.v[e] * (y1 > 0.0f ? 1.0f : slope);
         s1 += z0; s2 = fmaf(z0, d0, s2); t1 += z1; t2 = fmaf(z1, d1, t2);
       }
     }
@@ -372,7 +372,7 @@ __device__ __forceinline__ void warp_reduce_R(const FusedArgs &a, const RingGeom
       for (int e = 0; e < 4; ++e) {
         const float d0 = x0.v[e] - mean;
         const float y0 = fmaf(d0, scale, beta);
-        const float z0 = relu ? g0.v[e] * (y0 > 0.0f ? 1.0f : 0.0f) : g0.v[e];
+        const float z0 = g0.v[e] * (y0 > 0.0f ? 1.0f : slope);
         s1 += z0; s2 = fmaf(z0, d0, s2);
       }
     }
@@ -388,7 +388,8 @@ __device__ __forceinline__ void warp_apply_R(const FusedArgs &a, const RingGeom 
                                              const TileRange &tr, uint32_t slot, const float4 *coef, uint32_t coef_q)
 {
   const uint32_t tid = threadIdx.x, lane = tid & 31;
-  const bool relu = a.relu != 0, acc = a.accumulate != 0;
+  const float slope = a.neg_slope;      // activation: t * (t > 0 ? 1 : slope)
+  const bool acc = a.accumulate != 0;
   const uint64_t drop = policy_drop();
   const uint64_t rs = (uint64_t)a.plan.C * a.plan.dim0;
   float *out = a.out + tr.base;
@@ -409,7 +410,7 @@ __device__ __forceinline__ void warp_apply_R(const FusedArgs &a, const RingGeom 
     Pack<4> o;
     if constexpr (DIR == 0) {
 #pragma unroll
-      for (int e = 0; e < 4; ++e) { const float yb = fmaf(vx.v[e] - mean, scale, beta); o.v[e] = relu ? positive_clip(yb) : yb; }
+      for (int e = 0; e < 4; ++e) { const float yb = fmaf(vx.v[e] - mean, scale, beta); o.v[e] = yb * (yb > 0.0f ? 1.0f : slope); }
     } else {
       const Pack<4> vd = lds128(ad);
       if (acc) o = Pack<4>::load(dst);
@@ -417,7 +418,7 @@ __device__ __forceinline__ void warp_apply_R(const FusedArgs &a, const RingGeom 
       for (int e = 0; e < 4; ++e) {
         const float d = vx.v[e] - mean;
         const float yb = fmaf(d, scale, beta);
-        const float dz = relu ? vd.v[e] * (yb > 0.0f ? 1.0f : 0.0f) : vd.v[e];
+        const float dz = vd.v[e] * (yb > 0.0f ? 1.0f : slope);
         const float dx = fmaf(scale, dz, fmaf(cB, d, cC));
         o.v[e] = acc ? o.v[e] + dx : dx;
       }
@@ -441,7 +442,7 @@ __device__ __forceinline__ void block_reduce_S(const FusedArgs &a, const RingGeo
 {
   const uint32_t tid = threadIdx.x;
   const float *xs = slot_x(sm, g, slot);
-  const bool relu = a.relu != 0;
+  const float slope = a.neg_slope;      // activation: t * (t > 0 ? 1 : slope)
   {
     // regime S: thread owns float4 positions tid, tid+256 of the segment in every sample of the tile
     const uint32_t seg4 = tr.len / 4, seg = tr.len, d0 = a.plan.dim0;
@@ -516,7 +517,7 @@ __device__ __forceinline__ void block_reduce_S(const FusedArgs &a, const RingGeo
             for (int i = 0; i < 4; ++i) {
               const float d = px.v[i] - cm[k][i];
               const float yb = fmaf(d, cs[k][i], cbt[k][i]);
-              const float dz = relu ? pd.v[i] * (yb > 0.0f ? 1.0f : 0.0f) : pd.v[i];
+              const float dz = pd.v[i] * (yb > 0.0f ? 1.0f : slope);
               s1[k][i] += dz; s2[k][i] = fmaf(dz, d, s2[k][i]);
             }
           }
@@ -551,7 +552,8 @@ __device__ __forceinline__ void block_apply_S(const FusedArgs &a, const RingGeom
   const uint32_t tid = threadIdx.x;
   const float *xs = slot_x(sm, g, slot);
   const float *ds = slot_dy<DIR>(sm, g, slot);
-  const bool relu = a.relu != 0, acc = a.accumulate != 0;
+  const float slope = a.neg_slope;      // activation: t * (t > 0 ? 1 : slope)
+  const bool acc = a.accumulate != 0;
   const uint64_t drop = policy_drop();
   const uint64_t rs = (uint64_t)a.plan.C * a.plan.dim0;
   float *out = a.out + tr.base;
@@ -580,7 +582,7 @@ __device__ __forceinline__ void block_apply_S(const FusedArgs &a, const RingGeom
           Pack<4> o;
           if constexpr (DIR == 0) {
 #pragma unroll
-            for (int i = 0; i < 4; ++i) { const float yb = fmaf(px.v[i] - cm[k][i], cs[k][i], cbt[k][i]); o.v[i] = relu ? positive_clip(yb) : yb; }
+            for (int i = 0; i < 4; ++i) { const float yb = fmaf(px.v[i] - cm[k][i], cs[k][i], cbt[k][i]); o.v[i] = yb * (yb > 0.0f ? 1.0f : slope); }
           } else {
             const Pack<4> pd = lds4(ds + so);
             if (acc) o = Pack<4>::load(out + off);
@@ -588,7 +590,7 @@ __device__ __forceinline__ void block_apply_S(const FusedArgs &a, const RingGeom
             for (int i = 0; i < 4; ++i) {
               const float d = px.v[i] - cm[k][i];
               const float yb = fmaf(d, cs[k][i], cbt[k][i]);
-              const float dz = relu ? pd.v[i] * (yb > 0.0f ? 1.0f : 0.0f) : pd.v[i];
+              const float dz = pd.v[i] * (yb > 0.0f ? 1.0f : slope);
               const float dx = fmaf(cs[k][i], dz, fmaf(cB[k][i], d, cC[k][i]));
               o.v[i] = acc ? o.v[i] + dx : dx;
             }

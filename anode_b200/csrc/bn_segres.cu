@@ -68,7 +68,8 @@ __global__ void __launch_bounds__(kSegThreads) bn_segres_kernel(const FusedArgs 
   const uint32_t n0 = rank * g.rows;
   const uint32_t rows = n0 < N ? ((N - n0 < g.rows) ? (N - n0) : g.rows) : 0;
   const uint64_t rs = (uint64_t)C * dim0;
-  const bool relu = a.relu != 0, acc = a.accumulate != 0;
+  const float slope = a.neg_slope;      // activation: t * (t > 0 ? 1 : slope)
+  const bool acc = a.accumulate != 0;
 
   float *colA = reinterpret_cast<float *>(sm + g.off_col), *colB = colA + kSegColFloats;
   float *coef = reinterpret_cast<float *>(sm + g.off_coef);         // 8 floats per channel
@@ -166,7 +167,7 @@ __global__ void __launch_bounds__(kSegThreads) bn_segres_kernel(const FusedArgs 
           for (int i = 0; i < 4; ++i) {
             const float d = e[i] - cm[i];
             const float yb = fmaf(d, cs[i], cbt[i]);
-            const float dz = relu ? f[i] * (yb > 0.0f ? 1.0f : 0.0f) : f[i];
+            const float dz = f[i] * (yb > 0.0f ? 1.0f : slope);
             s1[i] += dz; s2[i] = fmaf(dz, d, s2[i]);
           }
         }
@@ -269,7 +270,7 @@ __global__ void __launch_bounds__(kSegThreads) bn_segres_kernel(const FusedArgs 
         float o[4];
         if (DIR == 0) {
 #pragma unroll
-          for (int i = 0; i < 4; ++i) { const float yb = fmaf(e[i] - cm[i], cs[i], cbt[i]); o[i] = relu ? positive_clip(yb) : yb; }
+          for (int i = 0; i < 4; ++i) { const float yb = fmaf(e[i] - cm[i], cs[i], cbt[i]); o[i] = yb * (yb > 0.0f ? 1.0f : slope); }
         } else {
           const float4 w = *reinterpret_cast<const float4 *>(pd + (size_t)r * Lw);
           const float f[4] = {w.x, w.y, w.z, w.w};
@@ -279,7 +280,7 @@ __global__ void __launch_bounds__(kSegThreads) bn_segres_kernel(const FusedArgs 
           for (int i = 0; i < 4; ++i) {
             const float d = e[i] - cm[i];
             const float yb = fmaf(d, cs[i], cbt[i]);
-            const float dz = relu ? f[i] * (yb > 0.0f ? 1.0f : 0.0f) : f[i];
+            const float dz = f[i] * (yb > 0.0f ? 1.0f : slope);
             const float dx = fmaf(cs[i], dz, fmaf(cB[i], d, cC[i]));
             o[i] = acc ? old[i] + dx : dx;
           }

@@ -333,9 +333,16 @@ class BatchNormalize2dFusedOp:
     """Forward: statistics, running averages, normalize, affine, ReLU in one launch."""
     @staticmethod
     def apply(axes, epsilon, avg_rate, x, y, mean, var, avg_mean=None, avg_var=None, gamma=None, beta=None,
-              relu=True, workspace=None, cfg=None, stream=None):
+              relu=True, workspace=None, cfg=None, stream=None, neg_slope=None):
         d0, c, n = dims_of(x, axes)
         ws = workspace if workspace is not None else Workspace(d0, c, n, x.device)
+        if neg_slope is not None:      # general activation t*(t > 0 ? 1 : neg_slope), e.g. leaky ReLU
+            check(_lib.load().anode_gpu_batch_norm_act_fused_fwd_3d1_packed_f32(
+                d0, c, n, ctypes.c_float(epsilon), ctypes.c_float(avg_rate), ctypes.c_float(neg_slope),
+                _p(x), _p(gamma), _p(beta), _p(y), _p(mean), _p(var), _p(avg_mean), _p(avg_var),
+                ws.ptr, ws.bytes, _cfg(cfg), _stream(stream)),
+                "anode_gpu_batch_norm_act_fused_fwd_3d1_packed_f32")
+            return y
         check(_lib.load().anode_gpu_batch_norm_relu_fused_fwd_3d1_packed_f32(
             d0, c, n, ctypes.c_float(epsilon), ctypes.c_float(avg_rate), int(bool(relu)),
             _p(x), _p(gamma), _p(beta), _p(y), _p(mean), _p(var), _p(avg_mean), _p(avg_var),
@@ -348,9 +355,16 @@ class BatchNormalize2dBwdFusedOp:
     """Backward: ReLU mask, both channel reductions, dgamma/dbeta and dx in one launch."""
     @staticmethod
     def apply(axes, dy, x, mean, var, dx, gamma=None, beta=None, dgamma=None, dbeta=None, relu=True,
-              cap=WriteCap.Assign, workspace=None, cfg=None, stream=None):
+              cap=WriteCap.Assign, workspace=None, cfg=None, stream=None, neg_slope=None):
         d0, c, n = dims_of(x, axes)
         ws = workspace if workspace is not None else Workspace(d0, c, n, x.device)
+        if neg_slope is not None:
+            check(_lib.load().anode_gpu_batch_norm_act_fused_bwd_3d1_packed_f32(
+                d0, c, n, ctypes.c_float(neg_slope), int(cap is WriteCap.Accumulate),
+                _p(dy), _p(x), _p(mean), _p(var), _p(gamma), _p(beta), _p(dx), _p(dgamma), _p(dbeta),
+                ws.ptr, ws.bytes, _cfg(cfg), _stream(stream)),
+                "anode_gpu_batch_norm_act_fused_bwd_3d1_packed_f32")
+            return dx
         check(_lib.load().anode_gpu_batch_norm_relu_fused_bwd_3d1_packed_f32(
             d0, c, n, int(bool(relu)), int(cap is WriteCap.Accumulate),
             _p(dy), _p(x), _p(mean), _p(var), _p(gamma), _p(beta), _p(dx), _p(dgamma), _p(dbeta),

@@ -222,6 +222,25 @@ int anode_gpu_batch_norm_relu_fused_bwd_3d1_packed_f32(
     void *workspace, size_t workspace_bytes,
     const struct KernelConfig *cfg, struct CUstream_st *stream);
 
+/* The two calls above with a general activation after the affine step,
+ *   act(t) = t * (t > 0 ? 1 : neg_slope):   0 = ReLU (the calls above with relu = 1), 1 = none
+ *   (relu = 0), c = leaky ReLU with constant c, the reference's LeakyReluFlatMap
+ *   y = (mask + (1-mask)*c)*x and its adjoint dx = (mask + (1-mask)*c)*dy (flat_map.cu:44-69). */
+int anode_gpu_batch_norm_act_fused_fwd_3d1_packed_f32(
+    uint32_t dim0, uint32_t dim1, uint32_t dim2,
+    float epsilon, float avg_rate, float neg_slope,
+    const float *x, const float *gamma, const float *beta,
+    float *y, float *mean, float *var, float *run_mean, float *run_var,
+    void *workspace, size_t workspace_bytes,
+    const struct KernelConfig *cfg, struct CUstream_st *stream);
+int anode_gpu_batch_norm_act_fused_bwd_3d1_packed_f32(
+    uint32_t dim0, uint32_t dim1, uint32_t dim2, float neg_slope, int accumulate,
+    const float *dy, const float *x, const float *mean, const float *var,
+    const float *gamma, const float *beta,
+    float *dx, float *dgamma, float *dbeta,
+    void *workspace, size_t workspace_bytes,
+    const struct KernelConfig *cfg, struct CUstream_st *stream);
+
 /* Forward pass for callers that have no scratch memory to give.  No counterpart in the
  * reference.  Same arguments and results as anode_gpu_batch_norm_relu_fused_fwd_3d1_packed_f32
  * minus the workspace: anode's op closures pass only dimensions, inputs, pre-made outputs, a

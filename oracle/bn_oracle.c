@@ -323,6 +323,27 @@ ORACLE_API void oracle_positive_clip_bwd_f32(size_t len, const float *dy, const 
   for (size_t i = 0; i < len; ++i) dx[i] = dy[i] * ((float)(y[i] > 0.0f));
 }
 
+/* flat_map.cu:44-52: y = (mask + (1 - mask)*c) * x with mask = (float)(x > 0)   (leaky ReLU) */
+ORACLE_API void oracle_leaky_relu_f32(size_t len, float c, const float *x, float *y)
+{
+#pragma omp parallel for schedule(static)
+  for (size_t i = 0; i < len; ++i) {
+    float xi = x[i];
+    float mask = (float)(xi > 0.0f);
+    y[i] = (mask + (1.0f - mask) * c) * xi;
+  }
+}
+
+/* flat_map.cu:61-69: dx = (mask + (1 - mask)*c) * dy with mask = (float)(y > 0) */
+ORACLE_API void oracle_leaky_relu_bwd_f32(size_t len, float c, const float *dy, const float *y, float *dx)
+{
+#pragma omp parallel for schedule(static)
+  for (size_t i = 0; i < len; ++i) {
+    float mask = (float)(y[i] > 0.0f);
+    dx[i] = (mask + (1.0f - mask) * c) * dy[i];
+  }
+}
+
 /* Running statistic update, pinned by tests/test_gpu.rs:561-593: y <- y + r*(x - y). */
 ORACLE_API void oracle_online_average_f32(uint32_t len, float rate, const float *x, float *y)
 {
@@ -408,8 +429,26 @@ ORACLE_API void oracle_bn_relu_fwd_bwd_f32(
 
 /* Same layer in double precision (inputs f32, every intermediate and output f64).
  * Channels are independent, so one pass per channel does the whole thing. */
+ORACLE_API void oracle_bn_act_fwd_bwd_f64(
+    uint32_t dim0, uint32_t dim1, uint32_t dim2, double epsilon, double avg_rate, double neg_slope,
+    const float *x, const float *dy, const float *gamma, const float *beta,
+    double *run_mean, double *run_var, double *y, double *dx,
+    double *mean, double *var, double *dgamma, double *dbeta);
+
 ORACLE_API void oracle_bn_relu_fwd_bwd_f64(
     uint32_t dim0, uint32_t dim1, uint32_t dim2, double epsilon, double avg_rate,
+    const float *x, const float *dy, const float *gamma, const float *beta,
+    double *run_mean, double *run_var, double *y, double *dx,
+    double *mean, double *var, double *dgamma, double *dbeta)
+{
+  oracle_bn_act_fwd_bwd_f64(dim0, dim1, dim2, epsilon, avg_rate, 0.0, x, dy, gamma, beta, run_mean, run_var, y, dx,
+                            mean, var, dgamma, dbeta);
+}
+
+/* The same with the activation act(t) = t*(t > 0 ? 1 : neg_slope): 0 is the ReLU above, c the
+ * reference's leaky ReLU (flat_map.cu:44-69), 1 no activation. */
+ORACLE_API void oracle_bn_act_fwd_bwd_f64(
+    uint32_t dim0, uint32_t dim1, uint32_t dim2, double epsilon, double avg_rate, double neg_slope,
     const float *x, const float *dy, const float *gamma, const float *beta,
     double *run_mean, double *run_var, double *y, double *dx,
     double *mean, double *var, double *dgamma, double *dbeta)
@@ -441,9 +480,9 @@ ORACLE_API void oracle_bn_relu_fwd_bwd_f64(
       for (uint32_t i0 = 0; i0 < dim0; ++i0) {
         double xh = ((double)x[row + i0] - m) * r;
         double yb = g * xh + b;
-        double yy = yb > 0.0 ? yb : 0.0;
+        double yy = yb > 0.0 ? yb : neg_slope * yb;
         y[row + i0] = yy;
-        double dzz = yy > 0.0 ? (double)dy[row + i0] : 0.0;
+        double dzz = yb > 0.0 ? (double)dy[row + i0] : neg_slope * (double)dy[row + i0];
         sdz += dzz; sdzxh += dzz * xh;
       }
     }
@@ -460,7 +499,8 @@ ORACLE_API void oracle_bn_relu_fwd_bwd_f64(
     for (uint32_t n = 0; n < dim2; ++n) {
       const size_t row = pack3(0, dim0, c, dim1, n);
       for (uint32_t i0 = 0; i0 < dim0; ++i0) {
-        double dzz = y[row + i0] > 0.0 ? g * (double)dy[row + i0] : 0.0;
+        double yb = g * (((double)x[row + i0] - m) * r) + b;
+        double dzz = (yb > 0.0 ? 1.0 : neg_slope) * g * (double)dy[row + i0];
         dx[row + i0] = dzz * r + dvar * ((double)x[row + i0] - m) * 2.0 / M + dmean / M;
       }
     }

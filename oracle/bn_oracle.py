@@ -51,6 +51,9 @@ def lib():
             "oracle_online_average_f32": [_u32, _f32, _pf, _pf],
             "oracle_bn_relu_fwd_bwd_f32": [_u32, _u32, _u32, _f32, _f32] + [_pf] * 14 + [_u32],
             "oracle_bn_relu_fwd_bwd_f64": [_u32, _u32, _u32, _f64, _f64, _pf, _pf, _pf, _pf] + [_pd] * 8,
+            "oracle_bn_act_fwd_bwd_f64": [_u32, _u32, _u32, _f64, _f64, _f64, _pf, _pf, _pf, _pf] + [_pd] * 8,
+            "oracle_leaky_relu_f32": [ctypes.c_size_t, _f32, _pf, _pf],
+            "oracle_leaky_relu_bwd_f32": [ctypes.c_size_t, _f32, _pf, _pf, _pf],
         }
         for name, args in sig.items():
             fn = getattr(L, name)
@@ -182,6 +185,20 @@ def positive_clip_bwd(dy, y):
     return dx
 
 
+def leaky_relu(c, x):
+    """routines_gpu/flat_map.cu:44-52."""
+    y = np.empty_like(x)
+    lib().oracle_leaky_relu_f32(x.size, c, _p(x), _p(y))
+    return y
+
+
+def leaky_relu_bwd(c, dy, y):
+    """routines_gpu/flat_map.cu:61-69."""
+    dx = np.empty_like(dy)
+    lib().oracle_leaky_relu_bwd_f32(dy.size, c, _p(dy), _p(y), _p(dx))
+    return dx
+
+
 def online_average(rate, x, y):
     out = y.copy()
     lib().oracle_online_average_f32(x.size, rate, _p(x), _p(out))
@@ -218,7 +235,20 @@ def bn_relu_fwd_bwd_f64(x, dy, eps, avg_rate, run_mean, run_var, gamma=None, bet
     return dict(y=y, dx=dx, mean=mean, var=var, run_mean=rm, run_var=rv, dgamma=dg, dbeta=db)
 
 
-def numpy_truth(x, dy, eps, avg_rate, run_mean, run_var, gamma=None, beta=None):
+def bn_act_fwd_bwd_f64(x, dy, eps, avg_rate, run_mean, run_var, gamma=None, beta=None, neg_slope=0.0):
+    """float64 truth with the activation t*(t > 0 ? 1 : neg_slope) (0: ReLU, c: leaky ReLU, 1: none)."""
+    d0, c, n = dims_of(x.shape)
+    rm, rv = run_mean.astype(np.float64).copy(), run_var.astype(np.float64).copy()
+    y, dx = np.empty(x.shape, np.float64), np.empty(x.shape, np.float64)
+    mean, var = np.zeros(c), np.zeros(c)
+    dg, db = np.zeros(c), np.zeros(c)
+    lib().oracle_bn_act_fwd_bwd_f64(d0, c, n, eps, avg_rate, neg_slope, _p(x), _p(dy), _p(gamma), _p(beta),
+                                    _pd_(rm), _pd_(rv), _pd_(y), _pd_(dx), _pd_(mean), _pd_(var),
+                                    _pd_(dg), _pd_(db))
+    return dict(y=y, dx=dx, mean=mean, var=var, run_mean=rm, run_var=rv, dgamma=dg, dbeta=db)
+
+
+def numpy_truth(x, dy, eps, avg_rate, run_mean, run_var, gamma=None, beta=None, neg_slope=0.0):
     """Vectorised float64 restatement, written independently of the C code.
 
     mean/var: routines_gpu/batch_norm.cu:54,160 (biased, eps folded into var);
@@ -238,8 +268,8 @@ def numpy_truth(x, dy, eps, avg_rate, run_mean, run_var, gamma=None, beta=None):
     g = np.ones(c) if gamma is None else gamma.astype(np.float64)
     b = np.zeros(c) if (gamma is None or beta is None) else beta.astype(np.float64)
     ybn = xhat * g.reshape(bshape) + b.reshape(bshape)
-    y = np.where(ybn > 0, ybn, 0.0)
-    dz = np.where(y > 0, dy64, 0.0)
+    y = np.where(ybn > 0, ybn, neg_slope * ybn)
+    dz = np.where(ybn > 0, dy64, neg_slope * dy64)
     dbeta = dz.sum(axis=ax)
     dgamma = (dz * xhat).sum(axis=ax)
     dzg = dz * g.reshape(bshape)

@@ -177,3 +177,29 @@ def test_argument_errors(ops):
     assert rc == -3
     with pytest.raises(ValueError):
         ops.BatchMean2dOp.apply([1, 0], x, v)
+
+
+@pytest.mark.parametrize("shape", [(16, 8, 56, 56), (64, 96, 7, 7), (5, 3, 7, 7)])    # tiled, cluster and plain kernels
+@pytest.mark.parametrize("slope", [0.1, 1.0, 0.0])
+def test_general_activation_matches_float64(ops, shape, slope):
+    """Leaky ReLU (flat_map.cu:44-69) fused like the ReLU: t*(t > 0 ? 1 : slope)."""
+    d = make_inputs(shape, seed=17, loc=0.3, scale=1.5)
+    x = dev(d["x"]); dy = dev(d["dy"]); g = dev(d["gamma"]); b = dev(d["beta"])
+    c = shape[1]
+    axes = list(range(x.dim() - 2))
+    mean = torch.zeros(c, device="cuda"); var = torch.zeros(c, device="cuda")
+    rm = dev(d["run_mean"]); rv = dev(d["run_var"])
+    dg = torch.zeros(c, device="cuda"); db = torch.zeros(c, device="cuda")
+    y = torch.empty_like(x); dx = torch.empty_like(x)
+    ws = ops.Workspace(*ops.dims_of(x), x.device)
+    ops.BatchNormalize2dFusedOp.apply(axes, 1e-5, 0.1, x, y, mean, var, rm, rv, g, b, workspace=ws, neg_slope=slope)
+    ops.BatchNormalize2dBwdFusedOp.apply(axes, dy, x, mean, var, dx, g, b, dg, db, workspace=ws, neg_slope=slope)
+    assert ws.status() == 0
+    got = dict(y=host(y), dx=host(dx), mean=host(mean), var=host(var), run_mean=host(rm), run_var=host(rv),
+               dgamma=host(dg), dbeta=host(db))
+    truth = o.bn_act_fwd_bwd_f64(d["x"], d["dy"], 1e-5, 0.1, d["run_mean"], d["run_var"], d["gamma"], d["beta"],
+                                 neg_slope=slope)
+    check_layer(got, truth, d["x"], d["gamma"], d["beta"], "slope %g " % slope)
+    if slope == 0.0:      # the same launch as relu = 1
+        ref, _ = run_fused(ops, d)
+        assert (ref["y"] == got["y"]).all() and (ref["dx"] == got["dx"]).all()

@@ -95,3 +95,24 @@ def test_golden_vectors_from_reference_kernels(path):
 
 def test_golden_vectors_present():
     assert glob.glob(os.path.join(GOLDEN, "ref_*.npz")), "tests/golden/ref_*.npz missing"
+
+
+def test_leaky_relu_literal_and_float64_variants_agree():
+    """The leaky-ReLU functors of the reference (flat_map.cu:44-69) and the float64 layer with a
+    negative slope: C against the independent numpy restatement, and slope 0 against the ReLU layer."""
+    x = np.array([-2.0, -0.0, 0.0, 0.5, 3.0], np.float32)
+    y = o.leaky_relu(0.1, x)
+    assert np.allclose(y, [-0.2, -0.0, 0.0, 0.5, 3.0])
+    dx = o.leaky_relu_bwd(0.1, np.ones_like(x), y)
+    assert np.allclose(dx, [0.1, 0.1, 0.1, 1.0, 1.0])
+    d = make_inputs((6, 5, 4, 3), seed=12, loc=0.3, scale=1.5)
+    args = (d["x"], d["dy"], 1e-5, 0.1, d["run_mean"], d["run_var"], d["gamma"], d["beta"])
+    for slope in (0.0, 0.1, 1.0):
+        c = o.bn_act_fwd_bwd_f64(*args, neg_slope=slope)
+        n = o.numpy_truth(*args, neg_slope=slope)
+        for k in c:
+            assert np.allclose(c[k], n[k], rtol=1e-9, atol=1e-11), (slope, k)
+    relu = o.bn_relu_fwd_bwd_f64(*args)
+    zero = o.bn_act_fwd_bwd_f64(*args, neg_slope=0.0)
+    for k in relu:
+        assert (relu[k] == zero[k]).all(), k
