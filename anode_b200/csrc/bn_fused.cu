@@ -217,6 +217,8 @@ int launch_best(FusedArgs &a, int dir, bool aligned, cudaStream_t stream)
     return launch_ring(a, g, dir, stream);
   }
   if (tunables().segres && segres_applies(a, dir, aligned) && launch_segres(a, dir, stream) == ANODE_OK) return ANODE_OK;
+  // the plain kernel has no cross-GPU exchange: a synchronized call in fused mode must not end up here
+  if (a.mode == MODE_FUSED && a.world > 1) return ANODE_E_LAUNCH;
   return launch_pipeline(a, dir, stream);
 }
 

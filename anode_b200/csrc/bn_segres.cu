@@ -14,6 +14,11 @@
 //   4. y (or dx) is computed from the slice still in shared memory and streamed out.
 // x (and dy) are read from HBM exactly once, nothing depends on L2 residency, there is no global
 // scratch, no flag and no spin-wait: the only synchronisation is the hardware cluster barrier.
+// (With several GPUs the per-channel records of the ranks are exchanged between steps 3 and 4 by
+// peer stores, and that wait is bounded.  A cluster waits for the peers' records of ITS unit only,
+// and the hardware dispatches clusters in index order on every GPU, so the lowest unfinished unit
+// anywhere is always being worked on everywhere; should a device ever dispatch differently, the
+// bounded wait turns it into a status bit, not a hang.)
 // Two blocks share an SM, so one block's copies overlap the other's arithmetic.
 //
 // Reference kernels this replaces on such shapes: routines_gpu/batch_norm.cu:24-57, 125-163,
@@ -50,6 +55,17 @@ __device__ __forceinline__ void cp_async16(void *smem_dst, const void *gsrc)
   const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(gsrc) : "memory");
 }
+__device__ __forceinline__ unsigned long long ld_sys_u64(const unsigned long long *p)
+{
+  unsigned long long v;
+  asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_sys_u64(unsigned long long *p, unsigned long long v)
+{
+  asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+constexpr long long kSegWaitCycles = 3000000000ll;      // bound of the wait for a peer's record: about 1.5 s
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void cp_async_wait_but_one() { asm volatile("cp.async.wait_group 1;" ::: "memory"); }
 
@@ -229,6 +245,42 @@ __global__ void __launch_bounds__(kSegThreads) bn_segres_kernel(const FusedArgs 
         if (DIR == 0) { const double n = (double)p.x, m = (double)p.y; t0 += n; t1 = fma(n, m, t1); t2 += (double)p.z + n * m * m; }
         else { t1 += (double)p.x; t2 += (double)p.y; }
       }
+      if (a.world > 1) {
+        // ---- several GPUs: the cluster's block 0 ships this GPU's record of the channel to every
+        // rank (plain 8-byte peer stores, each word tagged with the call's sequence number), every
+        // block collects the records of all ranks from its own GPU's buffer and merges them in
+        // rank order.  Same protocol and buffers as the tiled kernel (bn_ring.cuh, pull_merge_unit).
+        const size_t slot = ((((size_t)(a.epoch & 1u)) * a.world) * a.xchg_channels + c) * 4;
+        const size_t src_stride = (size_t)a.xchg_channels * 4;
+        if (rank == 0) {
+          float w0, w1, w2;
+          if (DIR == 0) { const double mean = t1 / t0; w0 = (float)t0; w1 = (float)mean; w2 = (float)fmax(t2 - t1 * mean, 0.0); }
+          else { w0 = (float)t1; w1 = (float)t2; w2 = 0.f; }
+          const unsigned long long e = (unsigned long long)a.epoch << 32;
+          for (uint32_t r = 0; r < a.world; ++r) {
+            unsigned long long *dst = a.xchg[r] + slot + a.rank * src_stride;
+            st_sys_u64(dst + 0, e | __float_as_uint(w0));
+            st_sys_u64(dst + 1, e | __float_as_uint(w1));
+            st_sys_u64(dst + 2, e | __float_as_uint(w2));
+          }
+        }
+        t0 = 0.0; t1 = 0.0; t2 = 0.0;
+        const long long w_start = clock64();
+        for (uint32_t r = 0; r < a.world; ++r) {
+          const unsigned long long *src = a.xchg[a.rank] + slot + r * src_stride;
+          unsigned long long v0, v1, v2;
+          for (;;) {
+            v0 = ld_sys_u64(src + 0); v1 = ld_sys_u64(src + 1); v2 = ld_sys_u64(src + 2);
+            if ((uint32_t)(v0 >> 32) == a.epoch && (uint32_t)(v1 >> 32) == a.epoch && (uint32_t)(v2 >> 32) == a.epoch) break;
+            if (clock64() - w_start > kSegWaitCycles) { atomicOr(a.status, ANODE_ST_WAIT_PEER); break; }   // give up, leave a mark
+            __nanosleep(200);
+          }
+          const double f0 = (double)__uint_as_float((uint32_t)v0), f1 = (double)__uint_as_float((uint32_t)v1);
+          const double f2 = (double)__uint_as_float((uint32_t)v2);
+          if (DIR == 0) { t0 += f0; t1 = fma(f0, f1, t1); t2 += f2 + f0 * f1 * f1; }
+          else { t1 += f0; t2 += f1; }
+        }
+      }
       if (DIR == 0) {
         const double mean = t1 / t0, m2 = fmax(t2 - t1 * mean, 0.0);
         const float mf = (float)mean;
@@ -353,7 +405,7 @@ static bool seg_geom(uint32_t dim0, uint32_t C, uint32_t N, int dir, SegGeom &g)
 bool segres_applies(const FusedArgs &a, int dir, bool aligned)
 {
   SegGeom g;
-  return aligned && a.mode == MODE_FUSED && a.world <= 1 && seg_geom(a.plan.dim0, a.plan.C, a.plan.N, dir, g);
+  return aligned && a.mode == MODE_FUSED && seg_geom(a.plan.dim0, a.plan.C, a.plan.N, dir, g);
 }
 
 // Launches the segments kernel for a prepared call.  ANODE_E_LAUNCH when the device refuses the

@@ -94,7 +94,9 @@ static int run_sync(FusedArgs &a, int dir, bool aligned, AnodeSyncComm *comm, si
 {
   const NcclApi &api = nccl();
   if (!comm) return ANODE_E_COMM;
-  if (comm->world > 1 && comm->xchg_channels >= a.plan.C && ring_applies(a, dir, aligned)) {
+  FusedArgs probe = a;
+  probe.mode = MODE_FUSED;
+  if (comm->world > 1 && comm->xchg_channels >= a.plan.C && (ring_applies(a, dir, aligned) || (tunables().segres && segres_applies(probe, dir, aligned)))) {
     // One kernel per direction: the block that owns a channel's first tile stores this GPU's
     // record into every rank's exchange buffer (plain peer stores over NVLink), every block reads
     // the records of all ranks from its own GPU's buffer.  No collective call, no extra launches.
