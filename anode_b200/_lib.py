@@ -55,6 +55,10 @@ SIGNATURES = {
         (c_int, _D + [f32, f32, f32] + [vp] * 8 + [vp, size_t] + _T),
     "anode_gpu_batch_norm_act_fused_bwd_3d1_packed_f32":
         (c_int, _D + [f32, c_int] + [vp] * 9 + [vp, size_t] + _T),
+    "anode_gpu_batch_norm_add_act_fused_fwd_3d1_packed_f32":
+        (c_int, _D + [f32, f32, f32] + [vp] * 9 + [vp, size_t] + _T),
+    "anode_gpu_batch_norm_add_act_fused_bwd_3d1_packed_f32":
+        (c_int, _D + [f32, c_int] + [vp] * 11 + [vp, size_t] + _T),
     "anode_gpu_batch_norm_relu_fused_fwd_static_3d1_packed_f32":
         (c_int, _D + [f32, f32, c_int] + [vp] * 8 + _T),
     "anode_gpu_batch_norm_host_step_staging_bytes": (size_t, _D + [u32]),

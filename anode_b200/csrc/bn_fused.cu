@@ -212,6 +212,11 @@ bool ring_applies(const FusedArgs &a, int dir, bool aligned)
 int launch_best(FusedArgs &a, int dir, bool aligned, cudaStream_t stream)
 {
   Plan rp; RingGeom g;
+  if (a.res || a.ymask || a.dres) {
+    // the residual epilogue exists in the plain kernel only
+    if (a.mode == MODE_FUSED && a.world > 1) return ANODE_E_LAUNCH;
+    return launch_pipeline(a, dir, stream);
+  }
   if (ring_plan_for(a.plan.dim0, a.plan.C, a.plan.N, aligned, dir, rp, g) && rp.ws_bytes <= a.ws_capacity) {
     a.plan = rp;
     return launch_ring(a, g, dir, stream);
@@ -422,6 +427,51 @@ extern "C" int anode_gpu_batch_norm_act_fused_bwd_3d1_packed_f32(
   if (rc) return rc;
   a.neg_slope = neg_slope;
   return launch_best(a, 1, aligned16(x) && aligned16(dy) && aligned16(dx), stream);
+}
+
+// Residual block epilogue: y = act(bn(x) + residual), the step after batch-norm in every residual
+// block (examples/run_imagenet_mpi.rs:191-195, 224-226: sum of the shortcut and the normalized
+// branch, then positive_clip).  Backward: the mask comes from the saved output y (as the reference's
+// positive_clip adjoint takes it, flat_map.cu:187-194), dresidual = dy*mask is the gradient of the
+// shortcut (the sum's adjoint fans dz out to both inputs), dx / dgamma / dbeta as before.
+extern "C" int anode_gpu_batch_norm_add_act_fused_fwd_3d1_packed_f32(
+    uint32_t dim0, uint32_t dim1, uint32_t dim2, float epsilon, float avg_rate, float neg_slope,
+    const float *x, const float *residual, const float *gamma, const float *beta,
+    float *y, float *mean, float *var, float *run_mean, float *run_var,
+    void *workspace, size_t workspace_bytes, const struct KernelConfig *cfg, struct CUstream_st *stream)
+{
+  (void)cfg;
+  if (!residual) return ANODE_E_NULL;
+  if (!aligned4(residual)) return ANODE_E_ALIGN;
+  FusedArgs a;
+  const int rc = prepare_fwd(a, dim0, dim1, dim2, epsilon, avg_rate, 1, x, gamma, beta, y, mean, var,
+                             run_mean, run_var, workspace, workspace_bytes);
+  if (rc) return rc;
+  if (workspace_bytes < anode_gpu_batch_norm_fused_workspace_bytes(dim0, dim1, dim2)) return ANODE_E_WORKSPACE;
+  a.neg_slope = neg_slope;
+  a.res = residual;
+  if (!aligned16(residual)) a.plan = plan_for(dim0, dim1, dim2, false);      // scalar path
+  return launch_best(a, 0, aligned16(x) && aligned16(y) && aligned16(residual), stream);
+}
+
+extern "C" int anode_gpu_batch_norm_add_act_fused_bwd_3d1_packed_f32(
+    uint32_t dim0, uint32_t dim1, uint32_t dim2, float neg_slope, int accumulate,
+    const float *dy, const float *x, const float *y, const float *mean, const float *var,
+    const float *gamma, const float *beta, float *dx, float *dresidual, float *dgamma, float *dbeta,
+    void *workspace, size_t workspace_bytes, const struct KernelConfig *cfg, struct CUstream_st *stream)
+{
+  (void)cfg;
+  if (!y) return ANODE_E_NULL;
+  if (!aligned4(y) || (dresidual && !aligned4(dresidual))) return ANODE_E_ALIGN;
+  FusedArgs a;
+  const int rc = prepare_bwd(a, dim0, dim1, dim2, 1, accumulate, dy, x, mean, var, gamma, beta, dx,
+                             dgamma, dbeta, workspace, workspace_bytes);
+  if (rc) return rc;
+  a.neg_slope = neg_slope;
+  a.ymask = y; a.dres = dresidual;
+  const bool al = aligned16(x) && aligned16(dy) && aligned16(dx) && aligned16(y) && (!dresidual || aligned16(dresidual));
+  if (!al) a.plan = plan_for(dim0, dim1, dim2, false);
+  return launch_best(a, 1, al, stream);
 }
 
 extern "C" int anode_gpu_online_average_f32(uint32_t len, float rate, const float *x, float *y,

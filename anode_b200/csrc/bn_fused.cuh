@@ -32,6 +32,10 @@ struct FusedArgs {
   const float *dy;         // backward only
   const float *gamma, *beta;
   const float *mean_in, *var_in;   // backward only
+  // residual epilogue (plain kernel only): forward y = act(bn(x) + res); backward takes the mask
+  // from the saved output ymask and also writes dres = dy*mask
+  const float *res, *ymask;
+  float *dres;
   float *out;              // y (forward) or dx (backward)
   float *mean, *var, *run_mean, *run_var;   // forward outputs
   float *dgamma, *dbeta;   // backward outputs
@@ -297,9 +301,11 @@ __device__ __forceinline__ void apply_fwd_R(const FusedArgs &a, const TileRange 
     for (int u = 0; u < kUnroll; ++u) {
       const uint32_t j = j0 + u * kThreads;
       if (j < nvec) {
+        Pack<VEC> r = pack_fill<VEC>(0.f);
+        if (a.res) r = Pack<VEC>::load(a.res + off[u]);
 #pragma unroll
         for (int i = 0; i < VEC; ++i) {
-          const float yb = fmaf(v[u].v[i] - mean, scale, beta);
+          const float yb = fmaf(v[u].v[i] - mean, scale, beta) + r.v[i];
           v[u].v[i] = yb * (yb > 0.0f ? 1.0f : slope);
         }
         v[u].store(a.out + off[u], drop);
@@ -324,7 +330,7 @@ __device__ __forceinline__ void reduce_bwd_R(const FusedArgs &a, const TileRange
   const uint64_t keep = policy_keep();
   float s1 = 0.f, s2 = 0.f;
   for (uint32_t j0 = tid; j0 < nvec; j0 += kThreads * kUnroll) {
-    Pack<VEC> vx[kUnroll], vd[kUnroll];
+    Pack<VEC> vx[kUnroll], vd[kUnroll], vy[kUnroll];
 #pragma unroll
     for (int u = 0; u < kUnroll; ++u) {
       const uint32_t j = j0 + u * kThreads;
@@ -332,9 +338,11 @@ __device__ __forceinline__ void reduce_bwd_R(const FusedArgs &a, const TileRange
         const size_t off = vec_off<VEC>(tr, per_row, mul, rs, j);
         vx[u] = Pack<VEC>::load(a.x + off, keep);
         vd[u] = Pack<VEC>::load(a.dy + off, keep);
+        if (a.ymask) vy[u] = Pack<VEC>::load(a.ymask + off, keep);
       } else {
         vx[u] = pack_fill<VEC>(mean);
         vd[u] = pack_fill<VEC>(0.f);
+        vy[u] = pack_fill<VEC>(0.f);
       }
     }
 #pragma unroll
@@ -342,7 +350,7 @@ __device__ __forceinline__ void reduce_bwd_R(const FusedArgs &a, const TileRange
 #pragma unroll
       for (int i = 0; i < VEC; ++i) {
         const float d = vx[u].v[i] - mean;
-        const float yb = fmaf(d, scale, beta);
+        const float yb = a.ymask ? vy[u].v[i] : fmaf(d, scale, beta);
         // dz = dy * (float)(y > 0)  (routines_gpu/flat_map.cu:191-192)
         const float dz = vd[u].v[i] * (yb > 0.0f ? 1.0f : slope);
         s1 += dz; s2 = fmaf(dz, d, s2);
@@ -378,17 +386,20 @@ __device__ __forceinline__ void apply_bwd_R(const FusedArgs &a, const TileRange 
     for (int u = 0; u < kUnroll; ++u) {
       const uint32_t j = j0 + u * kThreads;
       if (j < nvec) {
-        Pack<VEC> o;
+        Pack<VEC> o, vy, r;
         if (acc) o = Pack<VEC>::load(a.out + off[u]);
+        if (a.ymask) vy = Pack<VEC>::load(a.ymask + off[u], drop);
 #pragma unroll
         for (int i = 0; i < VEC; ++i) {
           const float d = vx[u].v[i] - mean;
-          const float yb = fmaf(d, scale, beta);
+          const float yb = a.ymask ? vy.v[i] : fmaf(d, scale, beta);
           const float dz = vd[u].v[i] * (yb > 0.0f ? 1.0f : slope);
           const float dx = fmaf(scale, dz, fmaf(cB, d, cC));
           o.v[i] = acc ? o.v[i] + dx : dx;
+          r.v[i] = dz;
         }
         o.store(a.out + off[u], drop);
+        if (a.dres) r.store(a.dres + off[u], drop);
       }
     }
   }
@@ -508,7 +519,7 @@ __device__ __forceinline__ void reduce_bwd_S(const FusedArgs &a, const TileRange
   const float *bx = a.x + tr.base, *bd = a.dy + tr.base;
   constexpr int U = 2;
   for (uint32_t r0 = 0; r0 < tr.rows; r0 += U) {
-    Pack<4> px[U][kSegSlots], pd[U][kSegSlots];
+    Pack<4> px[U][kSegSlots], pd[U][kSegSlots], py[U][kSegSlots];
 #pragma unroll
     for (int u = 0; u < U; ++u)
 #pragma unroll
@@ -517,9 +528,10 @@ __device__ __forceinline__ void reduce_bwd_S(const FusedArgs &a, const TileRange
         if (r0 + u < tr.rows && v < seg4) {
           const size_t off = (size_t)(r0 + u) * rs + 4 * (size_t)v;
           px[u][k] = Pack<4>::load(bx + off); pd[u][k] = Pack<4>::load(bd + off);
+          if (a.ymask) py[u][k] = Pack<4>::load(a.ymask + tr.base + off);
         } else {
 #pragma unroll
-          for (int i = 0; i < 4; ++i) { px[u][k].v[i] = cm[k][i]; pd[u][k].v[i] = 0.f; }
+          for (int i = 0; i < 4; ++i) { px[u][k].v[i] = cm[k][i]; pd[u][k].v[i] = 0.f; py[u][k].v[i] = 0.f; }
         }
       }
 #pragma unroll
@@ -529,7 +541,7 @@ __device__ __forceinline__ void reduce_bwd_S(const FusedArgs &a, const TileRange
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
           const float d = px[u][k].v[i] - cm[k][i];
-          const float yb = fmaf(d, cs[k][i], cb[k][i]);
+          const float yb = a.ymask ? py[u][k].v[i] : fmaf(d, cs[k][i], cb[k][i]);
           const float dz = pd[u][k].v[i] * (yb > 0.0f ? 1.0f : slope);
           s1[k][i] += dz; s2[k][i] = fmaf(dz, d, s2[k][i]);
         }
@@ -595,21 +607,27 @@ __device__ __forceinline__ void apply_S(const FusedArgs &a, const TileRange &tr,
         const uint32_t v = tid + k * kThreads;
         if (r0 + u < tr.rows && v < seg4) {
           const size_t off = (size_t)(r0 + u) * rs + 4 * (size_t)v;
-          Pack<4> o;
+          Pack<4> o, e = pack_fill<4>(0.f), r;       // e: residual (forward) or saved output (backward)
           if (DIR == 1 && acc) o = Pack<4>::load(bo + off);
+          if (DIR == 0 && a.res) e = Pack<4>::load(a.res + tr.base + off);
+          if (DIR == 1 && a.ymask) e = Pack<4>::load(a.ymask + tr.base + off);
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
             const float d = px[u][k].v[i] - cm[k][i];
             const float yb = fmaf(d, cs[k][i], cb[k][i]);
             if (DIR == 0) {
-              o.v[i] = yb * (yb > 0.0f ? 1.0f : slope);
+              const float t = yb + e.v[i];
+              o.v[i] = t * (t > 0.0f ? 1.0f : slope);
             } else {
-              const float dz = pd[u][k].v[i] * (yb > 0.0f ? 1.0f : slope);
+              const float t = a.ymask ? e.v[i] : yb;
+              const float dz = pd[u][k].v[i] * (t > 0.0f ? 1.0f : slope);
               const float dx = fmaf(cs[k][i], dz, fmaf(cB[k][i], d, cC[k][i]));
               o.v[i] = acc ? o.v[i] + dx : dx;
+              r.v[i] = dz;
             }
           }
           o.store_stream(bo + off);
+          if (DIR == 1 && a.dres) r.store_stream(a.dres + tr.base + off);
         }
       }
   }

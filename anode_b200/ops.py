@@ -373,6 +373,32 @@ class BatchNormalize2dBwdFusedOp:
         return dx
 
 
+class BatchNormalize2dAddActFusedOp:
+    """Residual-block epilogue y = act(bn(x) + residual) and its adjoint (mask from the saved y,
+    dresidual = dy*mask), examples/run_imagenet_mpi.rs:191-195, 224-226."""
+    @staticmethod
+    def apply(axes, epsilon, avg_rate, x, residual, y, mean, var, avg_mean=None, avg_var=None, gamma=None, beta=None,
+              neg_slope=0.0, workspace=None, cfg=None, stream=None):
+        d0, c, n = dims_of(x, axes)
+        ws = workspace if workspace is not None else Workspace(d0, c, n, x.device)
+        check(_lib.load().anode_gpu_batch_norm_add_act_fused_fwd_3d1_packed_f32(
+            d0, c, n, ctypes.c_float(epsilon), ctypes.c_float(avg_rate), ctypes.c_float(neg_slope),
+            _p(x), _p(residual), _p(gamma), _p(beta), _p(y), _p(mean), _p(var), _p(avg_mean), _p(avg_var),
+            ws.ptr, ws.bytes, _cfg(cfg), _stream(stream)), "anode_gpu_batch_norm_add_act_fused_fwd_3d1_packed_f32")
+        return y
+
+    @staticmethod
+    def adjoint(axes, dy, x, y, mean, var, dx, dresidual=None, gamma=None, beta=None, dgamma=None, dbeta=None,
+                neg_slope=0.0, cap=WriteCap.Assign, workspace=None, cfg=None, stream=None):
+        d0, c, n = dims_of(x, axes)
+        ws = workspace if workspace is not None else Workspace(d0, c, n, x.device)
+        check(_lib.load().anode_gpu_batch_norm_add_act_fused_bwd_3d1_packed_f32(
+            d0, c, n, ctypes.c_float(neg_slope), int(cap is WriteCap.Accumulate),
+            _p(dy), _p(x), _p(y), _p(mean), _p(var), _p(gamma), _p(beta), _p(dx), _p(dresidual), _p(dgamma), _p(dbeta),
+            ws.ptr, ws.bytes, _cfg(cfg), _stream(stream)), "anode_gpu_batch_norm_add_act_fused_bwd_3d1_packed_f32")
+        return dx, dresidual
+
+
 BatchNormalize3dFusedOp, BatchNormalize3dBwdFusedOp = BatchNormalize2dFusedOp, BatchNormalize2dBwdFusedOp
 
 

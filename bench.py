@@ -293,8 +293,43 @@ def bench_workload(ops, name, rank, world, steps, warmup, dist, device, sample_c
            "value": n_global / (ms * 1e-3), "clocks": clocks, "launches_per_step": layer.launches_per_step}
     if with_e2e:
         res["infer"] = bench_infer(layer, x, y, steps, warmup)
+        if world == 1:
+            res["residual_block"] = bench_residual(ops, layer, x, dy, y, dx, steps, warmup)
         res["e2e"] = bench_e2e(ops, layer, x, dy, y, dx, dist, device, min(steps, 3))
     return res
+
+
+def bench_residual(ops, layer, x, dy, y, dx, steps, warmup):
+    """Residual-block epilogue y = relu(bn(x) + shortcut), forward + backward (plain kernel):
+    12 + 20 algorithmic bytes per element (x, shortcut -> y; x, dy, y -> dx, dshortcut)."""
+    import torch
+    res = torch.randn_like(x)
+    dres = torch.empty_like(x)
+    axes = list(range(x.dim() - 2))
+    ws = ops.Workspace(*ops.dims_of(x), x.device)
+
+    def step():
+        ops.BatchNormalize2dAddActFusedOp.apply(axes, layer.epsilon, layer.avg_rate, x, res, y, layer.mean, layer.var,
+                                                layer.avg_mean, layer.avg_var, layer.gamma, layer.beta, 0.0, ws)
+        ops.BatchNormalize2dAddActFusedOp.adjoint(axes, dy, x, y, layer.mean, layer.var, dx, dres, layer.gamma, layer.beta,
+                                                  layer.dgamma, layer.dbeta, 0.0, workspace=ws)
+    for _ in range(max(warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+    k = max(5, steps // 3)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(k):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    assert ws.status() == 0
+    ms = e0.elapsed_time(e1) / k
+    peak, kind = hbm_peak()
+    gbs = 32.0 * x.numel() / (ms * 1e-3) / 1e9
+    del res, dres
+    return {"kernel": "bn_pipeline_kernel (plain) with residual epilogue", "ms_per_step": ms,
+            "elements_per_s": x.numel() / (ms * 1e-3), "achieved_gbs": gbs, "frac_of_hbm_peak": gbs / peak, "peak_kind": kind}
 
 
 def bench_infer(layer, x, y, steps, warmup):
@@ -431,6 +466,8 @@ def main():
         line["e2e"] = main_res["e2e"]
     if "infer" in main_res:
         line["infer"] = main_res["infer"]
+    if "residual_block" in main_res:
+        line["residual_block"] = main_res["residual_block"]
     tr = TRAFFIC.get(args.workload if world == 1 else "%s@%d" % (args.workload, world), {})
     for key, rk in (("bwd", "roofline"), ("fwd", "roofline_fwd")):
         if key in tr:

@@ -241,6 +241,27 @@ int anode_gpu_batch_norm_act_fused_bwd_3d1_packed_f32(
     void *workspace, size_t workspace_bytes,
     const struct KernelConfig *cfg, struct CUstream_st *stream);
 
+/* Residual-block epilogue: y = act(bn(x) + residual), act as above -- the step that follows
+ * batch-norm in every residual block (examples/run_imagenet_mpi.rs:191-195, 224-226: shortcut plus
+ * normalized branch, then positive_clip).  Backward: the mask is taken from the saved output y (as
+ * the reference's positive_clip adjoint does, flat_map.cu:187-194); dresidual = dy*mask is the
+ * gradient of the shortcut (may be NULL, may alias dy); dx, dgamma, dbeta as in the calls above.
+ * Served by the plain kernel (12 / 20 algorithmic bytes per element forward / backward). */
+int anode_gpu_batch_norm_add_act_fused_fwd_3d1_packed_f32(
+    uint32_t dim0, uint32_t dim1, uint32_t dim2,
+    float epsilon, float avg_rate, float neg_slope,
+    const float *x, const float *residual, const float *gamma, const float *beta,
+    float *y, float *mean, float *var, float *run_mean, float *run_var,
+    void *workspace, size_t workspace_bytes,
+    const struct KernelConfig *cfg, struct CUstream_st *stream);
+int anode_gpu_batch_norm_add_act_fused_bwd_3d1_packed_f32(
+    uint32_t dim0, uint32_t dim1, uint32_t dim2, float neg_slope, int accumulate,
+    const float *dy, const float *x, const float *y, const float *mean, const float *var,
+    const float *gamma, const float *beta,
+    float *dx, float *dresidual, float *dgamma, float *dbeta,
+    void *workspace, size_t workspace_bytes,
+    const struct KernelConfig *cfg, struct CUstream_st *stream);
+
 /* Forward pass for callers that have no scratch memory to give.  No counterpart in the
  * reference.  Same arguments and results as anode_gpu_batch_norm_relu_fused_fwd_3d1_packed_f32
  * minus the workspace: anode's op closures pass only dimensions, inputs, pre-made outputs, a

@@ -447,10 +447,29 @@ ORACLE_API void oracle_bn_relu_fwd_bwd_f64(
 
 /* The same with the activation act(t) = t*(t > 0 ? 1 : neg_slope): 0 is the ReLU above, c the
  * reference's leaky ReLU (flat_map.cu:44-69), 1 no activation. */
+ORACLE_API void oracle_bn_add_act_fwd_bwd_f64(
+    uint32_t dim0, uint32_t dim1, uint32_t dim2, double epsilon, double avg_rate, double neg_slope,
+    const float *x, const float *residual, const float *dy, const float *gamma, const float *beta,
+    double *run_mean, double *run_var, double *y, double *dx, double *dresidual,
+    double *mean, double *var, double *dgamma, double *dbeta);
+
 ORACLE_API void oracle_bn_act_fwd_bwd_f64(
     uint32_t dim0, uint32_t dim1, uint32_t dim2, double epsilon, double avg_rate, double neg_slope,
     const float *x, const float *dy, const float *gamma, const float *beta,
     double *run_mean, double *run_var, double *y, double *dx,
+    double *mean, double *var, double *dgamma, double *dbeta)
+{
+  oracle_bn_add_act_fwd_bwd_f64(dim0, dim1, dim2, epsilon, avg_rate, neg_slope, x, NULL, dy, gamma, beta, run_mean, run_var,
+                                y, dx, NULL, mean, var, dgamma, dbeta);
+}
+
+/* With a residual input added before the activation: y = act(bn(x) + residual), the block
+ * epilogue of examples/run_imagenet_mpi.rs:191-195, 224-226 (sum, then positive_clip); the sum's
+ * adjoint hands dz = dy*mask to both inputs, so dresidual = dz.  residual / dresidual may be NULL. */
+ORACLE_API void oracle_bn_add_act_fwd_bwd_f64(
+    uint32_t dim0, uint32_t dim1, uint32_t dim2, double epsilon, double avg_rate, double neg_slope,
+    const float *x, const float *residual, const float *dy, const float *gamma, const float *beta,
+    double *run_mean, double *run_var, double *y, double *dx, double *dresidual,
     double *mean, double *var, double *dgamma, double *dbeta)
 {
   const double M = (double)dim0 * (double)dim2;
@@ -479,10 +498,11 @@ ORACLE_API void oracle_bn_act_fwd_bwd_f64(
       const size_t row = pack3(0, dim0, c, dim1, n);
       for (uint32_t i0 = 0; i0 < dim0; ++i0) {
         double xh = ((double)x[row + i0] - m) * r;
-        double yb = g * xh + b;
+        double yb = g * xh + b + (residual ? (double)residual[row + i0] : 0.0);
         double yy = yb > 0.0 ? yb : neg_slope * yb;
         y[row + i0] = yy;
         double dzz = yb > 0.0 ? (double)dy[row + i0] : neg_slope * (double)dy[row + i0];
+        if (dresidual) dresidual[row + i0] = dzz;
         sdz += dzz; sdzxh += dzz * xh;
       }
     }
@@ -499,7 +519,7 @@ ORACLE_API void oracle_bn_act_fwd_bwd_f64(
     for (uint32_t n = 0; n < dim2; ++n) {
       const size_t row = pack3(0, dim0, c, dim1, n);
       for (uint32_t i0 = 0; i0 < dim0; ++i0) {
-        double yb = g * (((double)x[row + i0] - m) * r) + b;
+        double yb = g * (((double)x[row + i0] - m) * r) + b + (residual ? (double)residual[row + i0] : 0.0);
         double dzz = (yb > 0.0 ? 1.0 : neg_slope) * g * (double)dy[row + i0];
         dx[row + i0] = dzz * r + dvar * ((double)x[row + i0] - m) * 2.0 / M + dmean / M;
       }

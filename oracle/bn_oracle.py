@@ -52,6 +52,7 @@ def lib():
             "oracle_bn_relu_fwd_bwd_f32": [_u32, _u32, _u32, _f32, _f32] + [_pf] * 14 + [_u32],
             "oracle_bn_relu_fwd_bwd_f64": [_u32, _u32, _u32, _f64, _f64, _pf, _pf, _pf, _pf] + [_pd] * 8,
             "oracle_bn_act_fwd_bwd_f64": [_u32, _u32, _u32, _f64, _f64, _f64, _pf, _pf, _pf, _pf] + [_pd] * 8,
+            "oracle_bn_add_act_fwd_bwd_f64": [_u32, _u32, _u32, _f64, _f64, _f64, _pf, _pf, _pf, _pf, _pf] + [_pd] * 9,
             "oracle_leaky_relu_f32": [ctypes.c_size_t, _f32, _pf, _pf],
             "oracle_leaky_relu_bwd_f32": [ctypes.c_size_t, _f32, _pf, _pf, _pf],
         }
@@ -246,6 +247,19 @@ def bn_act_fwd_bwd_f64(x, dy, eps, avg_rate, run_mean, run_var, gamma=None, beta
                                     _pd_(rm), _pd_(rv), _pd_(y), _pd_(dx), _pd_(mean), _pd_(var),
                                     _pd_(dg), _pd_(db))
     return dict(y=y, dx=dx, mean=mean, var=var, run_mean=rm, run_var=rv, dgamma=dg, dbeta=db)
+
+
+def bn_add_act_fwd_bwd_f64(x, residual, dy, eps, avg_rate, run_mean, run_var, gamma=None, beta=None, neg_slope=0.0):
+    """float64 truth of the residual-block epilogue y = act(bn(x) + residual); also returns dresidual."""
+    d0, c, n = dims_of(x.shape)
+    rm, rv = run_mean.astype(np.float64).copy(), run_var.astype(np.float64).copy()
+    y, dx, dres = (np.empty(x.shape, np.float64) for _ in range(3))
+    mean, var = np.zeros(c), np.zeros(c)
+    dg, db = np.zeros(c), np.zeros(c)
+    lib().oracle_bn_add_act_fwd_bwd_f64(d0, c, n, eps, avg_rate, neg_slope, _p(x), _p(residual), _p(dy), _p(gamma), _p(beta),
+                                        _pd_(rm), _pd_(rv), _pd_(y), _pd_(dx), _pd_(dres), _pd_(mean), _pd_(var),
+                                        _pd_(dg), _pd_(db))
+    return dict(y=y, dx=dx, dresidual=dres, mean=mean, var=var, run_mean=rm, run_var=rv, dgamma=dg, dbeta=db)
 
 
 def numpy_truth(x, dy, eps, avg_rate, run_mean, run_var, gamma=None, beta=None, neg_slope=0.0):

@@ -6,7 +6,7 @@ import pytest
 import torch
 
 from oracle import bn_oracle as o
-from tests.util import assert_close, check_layer, make_inputs
+from tests.util import assert_close, assert_sum_close, check_layer, make_inputs
 
 pytestmark = pytest.mark.gpu
 
@@ -203,3 +203,39 @@ def test_general_activation_matches_float64(ops, shape, slope):
     if slope == 0.0:      # the same launch as relu = 1
         ref, _ = run_fused(ops, d)
         assert (ref["y"] == got["y"]).all() and (ref["dx"] == got["dx"]).all()
+
+
+@pytest.mark.parametrize("shape", [(16, 8, 56, 56), (64, 96, 7, 7), (5, 3, 7, 7), (2, 4, 8, 16, 16)])
+@pytest.mark.parametrize("slope", [0.0, 0.1])
+def test_residual_epilogue_matches_float64(ops, shape, slope):
+    """y = act(bn(x) + residual) and its adjoint (mask from the saved y, dresidual = dy*mask)."""
+    d = make_inputs(shape, seed=19, loc=0.3, scale=1.5)
+    res_h = np.random.default_rng(20).standard_normal(shape).astype(np.float32)
+    x = dev(d["x"]); dy = dev(d["dy"]); res = dev(res_h); g = dev(d["gamma"]); b = dev(d["beta"])
+    c = shape[1]
+    axes = list(range(x.dim() - 2))
+    mean = torch.zeros(c, device="cuda"); var = torch.zeros(c, device="cuda")
+    rm = dev(d["run_mean"]); rv = dev(d["run_var"])
+    dg = torch.zeros(c, device="cuda"); db = torch.zeros(c, device="cuda")
+    y = torch.empty_like(x); dx = torch.empty_like(x); dres = torch.empty_like(x)
+    ws = ops.Workspace(*ops.dims_of(x), x.device)
+    ops.BatchNormalize2dAddActFusedOp.apply(axes, 1e-5, 0.1, x, res, y, mean, var, rm, rv, g, b, slope, ws)
+    ops.BatchNormalize2dAddActFusedOp.adjoint(axes, dy, x, y, mean, var, dx, dres, g, b, dg, db, slope, workspace=ws)
+    assert ws.status() == 0
+    truth = o.bn_add_act_fwd_bwd_f64(d["x"], res_h, d["dy"], 1e-5, 0.1, d["run_mean"], d["run_var"], d["gamma"], d["beta"],
+                                     neg_slope=slope)
+    got = dict(y=host(y), dx=host(dx), mean=host(mean), var=host(var), run_mean=host(rm), run_var=host(rv),
+               dgamma=host(dg), dbeta=host(db))
+    # elements whose pre-activation is within 1e-5 of zero may take either side of the mask
+    bs = (1, c) + (1,) * (len(shape) - 2)
+    pre = ((d["x"].astype(np.float64) - truth["mean"].reshape(bs)) / np.sqrt(truth["var"]).reshape(bs)
+           * d["gamma"].astype(np.float64).reshape(bs) + d["beta"].astype(np.float64).reshape(bs) + res_h)
+    skip = np.abs(pre) < 1e-5
+    assert skip.mean() < 1e-3
+    for k in ("mean", "var", "run_mean", "run_var"):
+        assert_close(got[k], truth[k], k)
+    assert_close(got["y"], truth["y"], "y", skip=skip)
+    assert_close(got["dx"], truth["dx"], "dx", skip=skip)
+    assert_close(host(dres), truth["dresidual"], "dresidual", skip=skip)
+    assert_sum_close(got["dgamma"], truth["dgamma"], "dgamma")
+    assert_sum_close(got["dbeta"], truth["dbeta"], "dbeta")

@@ -116,3 +116,29 @@ def test_leaky_relu_literal_and_float64_variants_agree():
     zero = o.bn_act_fwd_bwd_f64(*args, neg_slope=0.0)
     for k in relu:
         assert (relu[k] == zero[k]).all(), k
+
+
+def test_residual_epilogue_oracle_against_numpy():
+    """y = act(bn(x) + residual); dresidual = dy*mask; everything else as in the plain layer with dz."""
+    d = make_inputs((6, 5, 4, 3), seed=13, loc=0.3, scale=1.5)
+    res = np.random.default_rng(14).standard_normal(d["x"].shape).astype(np.float32)
+    for slope in (0.0, 0.2):
+        got = o.bn_add_act_fwd_bwd_f64(d["x"], res, d["dy"], 1e-5, 0.1, d["run_mean"], d["run_var"], d["gamma"], d["beta"],
+                                       neg_slope=slope)
+        c = d["x"].shape[1]
+        bs = (1, c, 1, 1)
+        x64 = d["x"].astype(np.float64)
+        mean = x64.mean(axis=(0, 2, 3)); var = x64.var(axis=(0, 2, 3)) + 1e-5
+        xhat = (x64 - mean.reshape(bs)) / np.sqrt(var).reshape(bs)
+        pre = xhat * d["gamma"].astype(np.float64).reshape(bs) + d["beta"].astype(np.float64).reshape(bs) + res
+        mask = np.where(pre > 0, 1.0, slope)
+        dz = d["dy"].astype(np.float64) * mask
+        assert np.allclose(got["y"], pre * mask, rtol=1e-9, atol=1e-11)
+        assert np.allclose(got["dresidual"], dz, rtol=1e-12, atol=0)
+        assert np.allclose(got["dbeta"], dz.sum(axis=(0, 2, 3)), rtol=1e-9, atol=1e-10)
+        assert np.allclose(got["dgamma"], (dz * xhat).sum(axis=(0, 2, 3)), rtol=1e-9, atol=1e-9)
+        M = x64.size / c
+        dzg = dz * d["gamma"].astype(np.float64).reshape(bs)
+        r = (1.0 / np.sqrt(var)).reshape(bs)
+        dx = r * (dzg - dzg.sum(axis=(0, 2, 3)).reshape(bs) / M - xhat * (dzg * xhat).sum(axis=(0, 2, 3)).reshape(bs) / M)
+        assert np.allclose(got["dx"], dx, rtol=1e-8, atol=1e-10)
