@@ -42,7 +42,7 @@ DEFAULT = "cfg3_syncbn"
 # DRAM bytes per element (ncu dram__bytes_read.sum + dram__bytes_write.sum per launch / elements),
 # captured on a 16-channel case of the same per-channel geometry and scaled by elements (the
 # kernels stream channel by channel, so traffic is proportional to the channel count).
-TRAFFIC = {"cfg3_syncbn": {"fwd": 8.80, "bwd": 16.27}}
+TRAFFIC = {"cfg3_syncbn": {"fwd": 8.78, "bwd": 16.22}}
 TRAFFIC_SOURCE = "profiles/bn_ring_kernels_cfg3_syncbn.md section 3"
 SEED = 20240607
 BLOCKS = 8        # the global tensor is generated in 8 blocks along the sharded axis, whatever N is
