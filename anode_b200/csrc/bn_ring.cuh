@@ -144,61 +144,6 @@ __device__ __forceinline__ void bulk_g2s(void *dst, const void *src, uint32_t by
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;"
                ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)), "l"(policy) : "memory");
 }
-__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kConsumers) : "memory"); }
-// Barrier over the consumer warps that also ANDs a predicate, so that the decision to go on or
-// to give up after a bounded wait is the same in every consumer thread.
-__device__ __forceinline__ bool consumer_all(bool ok)
-{
-  uint32_t r;
-  asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.u32 p, %1, 0;\n\tbar.red.and.pred q, 1, %2, p;\n\tselp.u32 %0, 1, 0, q;\n\t}"
-               : "=r"(r) : "r"((uint32_t)ok), "n"(kConsumers) : "memory");
-  return r != 0;
-}
-
-__device__ __forceinline__ Pack<4> lds4(const float *p)
-{
-  const float4 t = *reinterpret_cast<const float4 *>(p);
-  Pack<4> r; r.v[0] = t.x; r.v[1] = t.y; r.v[2] = t.z; r.v[3] = t.w; return r;
-}
-
-// Block-wide (consumer warps only) merge / sum; results valid in thread 0 / all threads.
-__device__ __forceinline__ Moments consumer_merge(Moments a, float *buf)
-{
-  constexpr int kWarps = kConsumers / 32;
-  a = warp_merge(a);
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  consumer_sync();
-  if (lane == 0) { buf[warp] = a.n; buf[kWarps + warp] = a.mean; buf[2 * kWarps + warp] = a.m2; }
-  consumer_sync();
-  if (warp == 0) {
-    Moments b{0.f, 0.f, 0.f};
-    if (lane < kWarps) { b.n = buf[lane]; b.mean = buf[kWarps + lane]; b.m2 = buf[2 * kWarps + lane]; }
-#pragma unroll
-    for (int o = kWarps / 2; o > 0; o >>= 1) {
-      Moments c;
-      c.n = __shfl_down_sync(0xffffffffu, b.n, o);
-      c.mean = __shfl_down_sync(0xffffffffu, b.mean, o);
-      c.m2 = __shfl_down_sync(0xffffffffu, b.m2, o);
-      b = merge(b, c);
-    }
-    a = b;
-  }
-  return a;
-}
-__device__ __forceinline__ void consumer_sum2(float &a, float &b, float *buf)
-{
-  constexpr int kWarps = kConsumers / 32;
-  a = warp_sum(a); b = warp_sum(b);
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  consumer_sync();
-  if (lane == 0) { buf[warp] = a; buf[kWarps + warp] = b; }
-  consumer_sync();
-  float ta = 0.f, tb = 0.f;
-#pragma unroll
-  for (int w = 0; w < kWarps; ++w) { ta += buf[w]; tb += buf[kWarps + w]; }
-  a = ta; b = tb;
-}
-
 // ---- the block's schedule --------------------------------------------------------------------
 // Operation k of a block: steps s = 0, 1, ...; at step s first REDUCE tile s (if any is left), then
 // APPLY tile s - look (if s >= look).  Every role walks this same sequence with its own cursor.
@@ -435,174 +380,6 @@ __device__ __forceinline__ void warp_apply_R(const FusedArgs &a, const RingGeom 
   if (lane == 0) { mbar_arrive(&ctl->empty[slot]); mbar_arrive(&ctl->coef_empty[coef_q]); }
 }
 
-// ---- regime S: the eight warps work on a tile together (block barriers) -------------------------
-template <int DIR>
-__device__ __forceinline__ void block_reduce_S(const FusedArgs &a, const RingGeom &g, unsigned char *sm, RingCtl *ctl,
-                                               const TileRange &tr, uint32_t slot, float4 *res)
-{
-  const uint32_t tid = threadIdx.x;
-  const float *xs = slot_x(sm, g, slot);
-  const float slope = a.neg_slope;      // activation: t * (t > 0 ? 1 : slope)
-  {
-    // regime S: thread owns float4 positions tid, tid+256 of the segment in every sample of the tile
-    const uint32_t seg4 = tr.len / 4, seg = tr.len, d0 = a.plan.dim0;
-    float *sa = reinterpret_cast<float *>(sm + g.off_seg), *sb = sa + kSegMaxFloats;
-    if constexpr (DIR == 0) {
-      float K[kSegSlots][4], s[kSegSlots][4], q[kSegSlots][4];
-#pragma unroll
-      for (int k = 0; k < (int)kSegSlots; ++k) {
-        const uint32_t v = tid + k * kConsumers;
-        Pack<4> p = pack_fill<4>(0.f);
-        if (v < seg4) p = lds4(xs + 4 * (size_t)v);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) { K[k][i] = p.v[i]; s[k][i] = 0.f; q[k][i] = 0.f; }
-      }
-      for (uint32_t r = 1; r < tr.rows; ++r) {
-#pragma unroll
-        for (int k = 0; k < (int)kSegSlots; ++k) {
-          const uint32_t v = tid + k * kConsumers;
-          if (v < seg4) {
-            const Pack<4> p = lds4(xs + (size_t)r * seg + 4 * (size_t)v);
-#pragma unroll
-            for (int i = 0; i < 4; ++i) { const float d = p.v[i] - K[k][i]; s[k][i] += d; q[k][i] = fmaf(d, d, q[k][i]); }
-          }
-        }
-      }
-      __syncwarp(); if ((tid & 31) == 0) mbar_arrive(&ctl->empty[slot]);
-      const float nr = (float)tr.rows, inv = __fdividef(1.0f, nr);
-      consumer_sync();   // sa / sb free (previous tile's channel pass is over)
-#pragma unroll
-      for (int k = 0; k < (int)kSegSlots; ++k) {
-        const uint32_t v = tid + k * kConsumers;
-        if (v < seg4) {
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            sa[4 * v + i] = fmaf(s[k][i], inv, K[k][i]);
-            sb[4 * v + i] = fmaxf(q[k][i] - s[k][i] * s[k][i] * inv, 0.f);
-          }
-        }
-      }
-      consumer_sync();
-      for (uint32_t ci = tid; ci < tr.cw; ci += kConsumers) {
-        const float *pm = sa + ci * d0, *pq = sb + ci * d0;
-        float smn = 0.f;
-        for (uint32_t i = 0; i < d0; ++i) smn += pm[i];
-        const float mean = smn / (float)d0;
-        float m2 = 0.f, dev = 0.f;
-        for (uint32_t i = 0; i < d0; ++i) { const float d = pm[i] - mean; m2 += pq[i]; dev = fmaf(d, d, dev); }
-        res[ci] = make_float4(nr * (float)d0, mean, fmaf(nr, dev, m2), 0.f);
-      }
-      consumer_sync();
-    } else {
-      const float *ds = slot_dy<1>(sm, g, slot);
-      const float4 *side = slot_side<1>(sm, g, slot);
-      float cm[kSegSlots][4], cs[kSegSlots][4], cbt[kSegSlots][4], s1[kSegSlots][4], s2[kSegSlots][4];
-#pragma unroll
-      for (int k = 0; k < (int)kSegSlots; ++k) {
-        const uint32_t v = tid + k * kConsumers;
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const uint32_t ci = (v < seg4) ? (4 * v + i) / d0 : 0;
-          const float4 cf = side[ci];
-          cm[k][i] = cf.x; cs[k][i] = cf.y; cbt[k][i] = cf.z; s1[k][i] = 0.f; s2[k][i] = 0.f;
-        }
-      }
-      for (uint32_t r = 0; r < tr.rows; ++r) {
-#pragma unroll
-        for (int k = 0; k < (int)kSegSlots; ++k) {
-          const uint32_t v = tid + k * kConsumers;
-          if (v < seg4) {
-            const Pack<4> px = lds4(xs + (size_t)r * seg + 4 * (size_t)v), pd = lds4(ds + (size_t)r * seg + 4 * (size_t)v);
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              const float d = px.v[i] - cm[k][i];
-              const float yb = fmaf(d, cs[k][i], cbt[k][i]);
-              const float dz = pd.v[i] * (yb > 0.0f ? 1.0f : slope);
-              s1[k][i] += dz; s2[k][i] = fmaf(dz, d, s2[k][i]);
-            }
-          }
-        }
-      }
-      __syncwarp(); if ((tid & 31) == 0) mbar_arrive(&ctl->empty[slot]);
-      consumer_sync();
-#pragma unroll
-      for (int k = 0; k < (int)kSegSlots; ++k) {
-        const uint32_t v = tid + k * kConsumers;
-        if (v < seg4) {
-#pragma unroll
-          for (int i = 0; i < 4; ++i) { sa[4 * v + i] = s1[k][i]; sb[4 * v + i] = s2[k][i]; }
-        }
-      }
-      consumer_sync();
-      for (uint32_t ci = tid; ci < tr.cw; ci += kConsumers) {
-        const float *p1 = sa + ci * d0, *p2 = sb + ci * d0;
-        float t1 = 0.f, t2 = 0.f;
-        for (uint32_t i = 0; i < d0; ++i) { t1 += p1[i]; t2 += p2[i]; }
-        res[ci] = make_float4(t1, t2, 0.f, 0.f);
-      }
-      consumer_sync();
-    }
-  }
-}
-
-template <int DIR>
-__device__ __forceinline__ void block_apply_S(const FusedArgs &a, const RingGeom &g, unsigned char *sm, RingCtl *ctl,
-                                              const TileRange &tr, uint32_t slot, const float4 *coef, uint32_t coef_q)
-{
-  const uint32_t tid = threadIdx.x;
-  const float *xs = slot_x(sm, g, slot);
-  const float *ds = slot_dy<DIR>(sm, g, slot);
-  const float slope = a.neg_slope;      // activation: t * (t > 0 ? 1 : slope)
-  const bool acc = a.accumulate != 0;
-  const uint64_t drop = policy_drop();
-  const uint64_t rs = (uint64_t)a.plan.C * a.plan.dim0;
-  float *out = a.out + tr.base;
-  {
-    const uint32_t seg4 = tr.len / 4, seg = tr.len, d0 = a.plan.dim0;
-    float cm[kSegSlots][4], cs[kSegSlots][4], cbt[kSegSlots][4], cB[kSegSlots][4], cC[kSegSlots][4];
-#pragma unroll
-    for (int k = 0; k < (int)kSegSlots; ++k) {
-      const uint32_t v = tid + k * kConsumers;
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const uint32_t ci = (v < seg4) ? (4 * v + i) / d0 : 0;
-        const float4 c0 = coef[2 * ci];
-        cm[k][i] = c0.x; cs[k][i] = c0.y; cbt[k][i] = c0.z;
-        if constexpr (DIR == 1) { const float4 c1 = coef[2 * ci + 1]; cB[k][i] = c1.x; cC[k][i] = c1.y; }
-      }
-    }
-    __syncwarp(); if ((tid & 31) == 0) mbar_arrive(&ctl->coef_empty[coef_q]);
-    for (uint32_t r = 0; r < tr.rows; ++r) {
-#pragma unroll
-      for (int k = 0; k < (int)kSegSlots; ++k) {
-        const uint32_t v = tid + k * kConsumers;
-        if (v < seg4) {
-          const size_t so = (size_t)r * seg + 4 * (size_t)v, off = (size_t)r * rs + 4 * (size_t)v;
-          const Pack<4> px = lds4(xs + so);
-          Pack<4> o;
-          if constexpr (DIR == 0) {
-#pragma unroll
-            for (int i = 0; i < 4; ++i) { const float yb = fmaf(px.v[i] - cm[k][i], cs[k][i], cbt[k][i]); o.v[i] = yb * (yb > 0.0f ? 1.0f : slope); }
-          } else {
-            const Pack<4> pd = lds4(ds + so);
-            if (acc) o = Pack<4>::load(out + off);
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              const float d = px.v[i] - cm[k][i];
-              const float yb = fmaf(d, cs[k][i], cbt[k][i]);
-              const float dz = pd.v[i] * (yb > 0.0f ? 1.0f : slope);
-              const float dx = fmaf(cs[k][i], dz, fmaf(cB[k][i], d, cC[k][i]));
-              o.v[i] = acc ? o.v[i] + dx : dx;
-            }
-          }
-          o.store(out + off, drop);
-        }
-      }
-    }
-    __syncwarp(); if ((tid & 31) == 0) mbar_arrive(&ctl->empty[slot]);
-  }
-}
-
 // ======================================================================================
 // delivery warp: unit completion
 // ======================================================================================
@@ -673,40 +450,6 @@ __device__ __forceinline__ void warp_finish_unit_R(const FusedArgs &a, uint32_t 
   } else {
     s1 = warp_sum_all(s1); s2 = warp_sum_all(s2);
     if (lane == 0) finish_channel_bwd(a, u, s1, s2);
-  }
-}
-
-// Regime S: a block of channels with few partials each; one lane per channel, 32 channels at a time.
-template <int DIR>
-__device__ __forceinline__ void warp_finish_unit_S(const FusedArgs &a, uint32_t u)
-{
-  const Plan &P = a.plan;
-  const uint32_t lane = threadIdx.x & 31, T = P.tiles_per_unit;
-  const uint32_t c0 = u * P.cb;
-  const uint32_t cw = (P.C - c0 < P.cb) ? (P.C - c0) : P.cb;
-  const float4 *part = ws_f4(a, P.off_part) + (size_t)u * T * P.cb;
-  for (uint32_t cbase = 0; cbase < cw; cbase += 32) {
-    const uint32_t ci = cbase + lane;
-    const bool live = ci < cw;
-    Moments64 acc{0.0, 0.0, 0.0};
-    double s1 = 0.0, s2 = 0.0;
-    for (uint32_t k0 = 0; k0 < T; k0 += kFinBatch) {
-      float4 reg[kFinBatch];
-#pragma unroll
-      for (int i = 0; i < kFinBatch; ++i) {
-        const uint32_t k = k0 + i;
-        reg[i] = (live && k < T) ? __ldcg(part + (size_t)k * P.cb + ci) : make_float4(0.f, 0.f, 0.f, 0.f);
-      }
-#pragma unroll
-      for (int i = 0; i < kFinBatch; ++i) {
-        if constexpr (DIR == 0) acc = merge64(acc, Moments64{(double)reg[i].x, (double)reg[i].y, (double)reg[i].z});
-        else { s1 += (double)reg[i].x; s2 += (double)reg[i].y; }
-      }
-    }
-    if (live) {
-      if constexpr (DIR == 0) finish_channel_fwd(a, c0 + ci, acc.n, acc.mean, acc.m2);
-      else finish_channel_bwd(a, c0 + ci, s1, s2);
-    }
   }
 }
 
@@ -911,6 +654,8 @@ __device__ __forceinline__ bool pull_merge_unit(const FusedArgs &a, RingCtl *ctl
 template <int DIR, int REGIME>
 __global__ void __launch_bounds__(kRingThreads, 1) bn_ring_kernel(const FusedArgs a, const RingGeom g)
 {
+  // Short-row shapes (regime S) are served by the cluster kernel (bn_segres.cu) and the plain kernel.
+  static_assert(REGIME == 0, "the warp-specialised kernel handles whole-row tiles only");
   extern __shared__ __align__(128) unsigned char sm[];
   RingCtl *ctl = reinterpret_cast<RingCtl *>(sm);
   const Plan &P = a.plan;
@@ -948,15 +693,9 @@ __global__ void __launch_bounds__(kRingThreads, 1) bn_ring_kernel(const FusedArg
         RING_PROF(0)
         ok = ok && warp_wait(&ctl->full[slot], par, ctl, status, ANODE_ST_WAIT_STATS);
         RING_PROF(1)
-        if constexpr (REGIME == 0) {
-          if (!ok) break;                               // warps are independent: no barrier to honour
-          warp_reduce_R<DIR>(a, g, sm, ctl, tr, slot, res_box(sm, g, q));
-          if (lane == 0) mbar_arrive(&ctl->res_full[q]);
-        } else {
-          if (!consumer_all(ok)) break;                 // same decision in all eight warps
-          block_reduce_S<DIR>(a, g, sm, ctl, tr, slot, res_box(sm, g, q));
-          if (lane == 0) mbar_arrive(&ctl->res_full[q]);
-        }
+        if (!ok) break;                                 // warps are independent: no barrier to honour
+        warp_reduce_R<DIR>(a, g, sm, ctl, tr, slot, res_box(sm, g, q));
+        if (lane == 0) mbar_arrive(&ctl->res_full[q]);
         RING_PROF(3)
       } else {
         const uint32_t q = ncoef % kCoefQ, qpar = (ncoef / kCoefQ) & 1u; ++ncoef;
@@ -970,13 +709,8 @@ __global__ void __launch_bounds__(kRingThreads, 1) bn_ring_kernel(const FusedArg
         RING_PROF(4)
         ok = ok && warp_wait(&ctl->full[slot], par, ctl, status, ANODE_ST_WAIT_STATS);
         RING_PROF(5)
-        if constexpr (REGIME == 0) {
-          if (!ok) break;
-          warp_apply_R<DIR>(a, g, sm, ctl, tr, slot, coef_box(sm, g, P.cb, q), q);
-        } else {
-          if (!consumer_all(ok)) break;
-          block_apply_S<DIR>(a, g, sm, ctl, tr, slot, coef_box(sm, g, P.cb, q), q);
-        }
+        if (!ok) break;
+        warp_apply_R<DIR>(a, g, sm, ctl, tr, slot, coef_box(sm, g, P.cb, q), q);
         RING_PROF(7)
       }
     }
@@ -1057,7 +791,7 @@ __global__ void __launch_bounds__(kRingThreads, 1) bn_ring_kernel(const FusedArg
       const bool d_ok = lane < kResQ && jd < n_red && mbar_test(&ctl->res_full[jd % kResQ], (jd / kResQ) & 1u);
       const uint32_t d_mask = __ballot_sync(0xffffffffu, d_ok);
       uint32_t nd = __ffs(~d_mask) - 1;                               // in order: leading run of ones
-      if (REGIME == 0 && nd > kPerTurn) nd = kPerTurn;
+      if (nd > kPerTurn) nd = kPerTurn;
       RING_PROF(0)
       if (nd) {
         if constexpr (REGIME == 0) {
@@ -1128,7 +862,7 @@ __global__ void __launch_bounds__(kRingThreads, 1) bn_ring_kernel(const FusedArg
         while (lmask) {
           const uint32_t src = __ffs(lmask) - 1; lmask &= lmask - 1;
           const uint32_t u = __shfl_sync(0xffffffffu, unit, src);
-          if constexpr (REGIME == 0) warp_finish_unit_R<DIR>(a, u); else warp_finish_unit_S<DIR>(a, u);
+          warp_finish_unit_R<DIR>(a, u);
           if (lane == 0) done[u] = 0;
 #ifdef ANODE_RING_PROFILE
           if (lane == 0) { RING_TL(u, gtimer()) RING_TL(8192 + 2 * u, tl_pick) RING_TL(8192 + 2 * u + 1, tl_atom) }
