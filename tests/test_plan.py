@@ -105,3 +105,51 @@ def test_division_free_walk_equals_per_tile_ranges(d0, c, n):
             want = tile(d0, c, n, first + i * stride, True, resident=64, tile_floats=2048)
             got = dict(zip(["unit", "c0", "cw", "n0", "rows", "col0", "len", "base"], list(out[8 * i:8 * i + 8])))
             assert got == want, (first, stride, i)
+
+
+def test_cluster_kernel_geometry_invariants():
+    """Geometry of the cluster kernel for short rows (no GPU needed): a unit's runs are 16-byte
+    aligned, the cluster's blocks cover all samples, the slices fit the shared memory of a block."""
+    import ctypes
+    from anode_b200 import _lib
+    lib = _lib.load()
+    cases = [(49, 2048, 1024), (49, 2048, 128), (196, 1024, 256), (15, 260, 33), (16, 8, 4), (49, 96, 64), (1, 512, 64),
+             (9, 12, 7), (25, 64, 4096), (225, 4, 2)]
+    for d0, c, n in cases:
+        for direction in (0, 1):
+            out = (ctypes.c_uint32 * 6)()
+            assert lib.anode_gpu_batch_norm_segres_geometry(d0, c, n, direction, out) == 0
+            ok, cb, cluster, rows, units, smem = list(out)
+            kind = lib.anode_gpu_batch_norm_fused_kernel_kind(d0, c, n, direction)
+            if not ok:
+                assert kind in (0, 1)
+                continue
+            assert kind == 2
+            assert (cb * d0) % 4 == 0 or cb == c
+            assert cb * d0 <= 1024 and 1 <= cb <= max(c, 1)
+            assert units == -(-c // cb)
+            assert cluster in (1, 2, 4, 8, 16) and rows * cluster >= n and rows * (cluster - 1) < n + rows
+            assert smem <= 227 * 1024
+            tensors = 2 if direction else 1
+            assert smem >= tensors * rows * min(cb, c) * d0 * 4
+    # long aligned rows belong to the tiled kernel, odd strides to the plain one
+    assert lib.anode_gpu_batch_norm_fused_kernel_kind(3136, 256, 2048, 0) == 1
+    assert lib.anode_gpu_batch_norm_fused_kernel_kind(117, 5, 3, 1) == 0
+
+
+def test_host_step_block_count_and_staging_size():
+    from anode_b200 import _lib
+    lib = _lib.load()
+    d0, c, n = 3136, 256, 2048
+    assert lib.anode_gpu_batch_norm_host_step_blocks(d0, c, n, 0) == 32          # 8 channels of 25.7 MB per block
+    assert lib.anode_gpu_batch_norm_host_step_blocks(d0, c, n, 100) == 3         # 100 + 100 + 56
+    assert lib.anode_gpu_batch_norm_host_step_blocks(d0, c, n, 1000) == 1
+    assert lib.anode_gpu_batch_norm_host_step_blocks(0, c, n, 0) == 0
+    small = lib.anode_gpu_batch_norm_host_step_staging_bytes(d0, c, n, 4)
+    big = lib.anode_gpu_batch_norm_host_step_staging_bytes(d0, c, n, 8)
+    assert 0 < small < big
+    # three buffers of three tensors of one block each, plus the workspace
+    assert big >= 9 * 8 * d0 * n * 4
+    rc = lib.anode_gpu_batch_norm_relu_fused_step_host_3d1_packed_f32(d0, c, n, 1e-5, 0.1, 1, None, None, None, None, None, None,
+                                                                      None, None, None, None, None, None, None, 0, 0, None, None)
+    assert rc == -1
