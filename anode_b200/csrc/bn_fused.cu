@@ -213,8 +213,9 @@ int launch_best(FusedArgs &a, int dir, bool aligned, cudaStream_t stream)
 {
   Plan rp; RingGeom g;
   if (a.res || a.ymask || a.dres) {
-    // the residual epilogue exists in the plain kernel only
+    // the residual epilogue exists in the cluster kernel (short rows) and in the plain kernel
     if (a.mode == MODE_FUSED && a.world > 1) return ANODE_E_LAUNCH;
+    if (tunables().segres && segres_applies(a, dir, aligned) && launch_segres(a, dir, stream) == ANODE_OK) return ANODE_OK;
     return launch_pipeline(a, dir, stream);
   }
   if (ring_plan_for(a.plan.dim0, a.plan.C, a.plan.N, aligned, dir, rp, g) && rp.ws_bytes <= a.ws_capacity) {

@@ -47,7 +47,7 @@ struct SegGeom {
   uint32_t rows;        // samples per block
   uint32_t units;
   uint32_t stages;      // 1: one unit per cluster, several blocks per SM; 2: persistent, next unit's copies in flight
-  uint32_t off_col, off_coef, off_part, off_stage, stage_bytes, off_dy, smem_bytes;
+  uint32_t off_col, off_coef, off_part, off_stage, stage_bytes, off_dy, off_e, smem_bytes;   // off_e: residual (forward) / saved output (backward)
 };
 
 __device__ __forceinline__ void cp_async16(void *smem_dst, const void *gsrc)
@@ -97,6 +97,8 @@ __global__ void __launch_bounds__(kSegThreads) bn_segres_kernel(const FusedArgs 
     const uint32_t L4 = cw * dim0 / 4;
     float *sx = reinterpret_cast<float *>(sm + g.off_stage + (size_t)st * g.stage_bytes);
     float *sdy = reinterpret_cast<float *>(sm + g.off_stage + (size_t)st * g.stage_bytes + g.off_dy);
+    float *se = reinterpret_cast<float *>(sm + g.off_stage + (size_t)st * g.stage_bytes + g.off_e);
+    const float *extra = DIR == 0 ? a.res : a.ymask;       // residual epilogue: third (second) tensor of the slice
     const uint32_t total4 = rows * L4;
     const uint32_t row = tid / L4;
     uint32_t col = tid - row * L4;
@@ -109,6 +111,7 @@ __global__ void __launch_bounds__(kSegThreads) bn_segres_kernel(const FusedArgs 
     for (uint32_t i = tid; i < total4; i += kSegThreads) {
       cp_async16(sx + 4 * (size_t)i, a.x + off);
       if (DIR == 1) cp_async16(sdy + 4 * (size_t)i, a.dy + off);
+      if (extra) cp_async16(se + 4 * (size_t)i, extra + off);
       off += step; col += dcol;
       if (col >= L4) { col -= L4; off += wrap; }
     }
@@ -123,6 +126,8 @@ __global__ void __launch_bounds__(kSegThreads) bn_segres_kernel(const FusedArgs 
     const uint32_t Lw = cw * dim0, L4 = Lw / 4;                     // floats / float4s per sample in this unit
     const float *sx = reinterpret_cast<const float *>(sm + g.off_stage + (size_t)st * g.stage_bytes);
     const float *sdy = reinterpret_cast<const float *>(sm + g.off_stage + (size_t)st * g.stage_bytes + g.off_dy);
+    const float *se = reinterpret_cast<const float *>(sm + g.off_stage + (size_t)st * g.stage_bytes + g.off_e);
+    const bool has_e = (DIR == 0 ? a.res : a.ymask) != nullptr;
     float4 *part = parts + (size_t)st * g.cb;
 
     // the next unit's slice starts travelling now (its stage was released at the end of the last round)
@@ -171,18 +176,20 @@ __global__ void __launch_bounds__(kSegThreads) bn_segres_kernel(const FusedArgs 
           colB[grp * Lw + 4 * v + i] = fmaxf(q[i] - s[i] * s[i] * inv, 0.f);          // its M2
         }
       } else {
-        const float *pd = sdy + 4 * (size_t)v;
+        const float *pd = sdy + 4 * (size_t)v, *pe = se + 4 * (size_t)v;
         float cm[4], cs[4], cbt[4], s1[4] = {0.f, 0.f, 0.f, 0.f}, s2[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
         for (int i = 0; i < 4; ++i) { cm[i] = coef[8 * ch[i] + 0]; cs[i] = coef[8 * ch[i] + 1]; cbt[i] = coef[8 * ch[i] + 2]; }
         for (uint32_t r = grp; r < rows; r += G) {
           const float4 p = *reinterpret_cast<const float4 *>(px + (size_t)r * Lw);
           const float4 w = *reinterpret_cast<const float4 *>(pd + (size_t)r * Lw);
-          const float e[4] = {p.x, p.y, p.z, p.w}, f[4] = {w.x, w.y, w.z, w.w};
+          float4 m = make_float4(0.f, 0.f, 0.f, 0.f);
+          if (has_e) m = *reinterpret_cast<const float4 *>(pe + (size_t)r * Lw);
+          const float e[4] = {p.x, p.y, p.z, p.w}, f[4] = {w.x, w.y, w.z, w.w}, ym[4] = {m.x, m.y, m.z, m.w};
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
             const float d = e[i] - cm[i];
-            const float yb = fmaf(d, cs[i], cbt[i]);
+            const float yb = has_e ? ym[i] : fmaf(d, cs[i], cbt[i]);      // residual epilogue: the saved output carries the mask
             const float dz = f[i] * (yb > 0.0f ? 1.0f : slope);
             s1[i] += dz; s2[i] = fmaf(dz, d, s2[i]);
           }
@@ -314,15 +321,18 @@ __global__ void __launch_bounds__(kSegThreads) bn_segres_kernel(const FusedArgs 
         cm[i] = coef[8 * ch[i] + 0]; cs[i] = coef[8 * ch[i] + 1]; cbt[i] = coef[8 * ch[i] + 2];
         cB[i] = DIR == 1 ? coef[8 * ch[i] + 3] : 0.f; cC[i] = DIR == 1 ? coef[8 * ch[i] + 4] : 0.f;
       }
-      const float *px = sx + 4 * (size_t)v, *pd = sdy + 4 * (size_t)v;
+      const float *px = sx + 4 * (size_t)v, *pd = sdy + 4 * (size_t)v, *pe = se + 4 * (size_t)v;
       float *po = a.out + (size_t)n0 * rs + (size_t)c0 * dim0 + 4 * (size_t)v;
+      float *pr = a.dres ? a.dres + (size_t)n0 * rs + (size_t)c0 * dim0 + 4 * (size_t)v : nullptr;
       for (uint32_t r = grp; r < rows; r += G) {
         const float4 p = *reinterpret_cast<const float4 *>(px + (size_t)r * Lw);
-        const float e[4] = {p.x, p.y, p.z, p.w};
-        float o[4];
+        float4 m = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (has_e) m = *reinterpret_cast<const float4 *>(pe + (size_t)r * Lw);
+        const float e[4] = {p.x, p.y, p.z, p.w}, ex[4] = {m.x, m.y, m.z, m.w};
+        float o[4], dzs[4] = {0.f, 0.f, 0.f, 0.f};
         if (DIR == 0) {
 #pragma unroll
-          for (int i = 0; i < 4; ++i) { const float yb = fmaf(e[i] - cm[i], cs[i], cbt[i]); o[i] = yb * (yb > 0.0f ? 1.0f : slope); }
+          for (int i = 0; i < 4; ++i) { const float yb = fmaf(e[i] - cm[i], cs[i], cbt[i]) + ex[i]; o[i] = yb * (yb > 0.0f ? 1.0f : slope); }
         } else {
           const float4 w = *reinterpret_cast<const float4 *>(pd + (size_t)r * Lw);
           const float f[4] = {w.x, w.y, w.z, w.w};
@@ -331,13 +341,15 @@ __global__ void __launch_bounds__(kSegThreads) bn_segres_kernel(const FusedArgs 
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
             const float d = e[i] - cm[i];
-            const float yb = fmaf(d, cs[i], cbt[i]);
+            const float yb = has_e ? ex[i] : fmaf(d, cs[i], cbt[i]);
             const float dz = f[i] * (yb > 0.0f ? 1.0f : slope);
             const float dx = fmaf(cs[i], dz, fmaf(cB[i], d, cC[i]));
             o[i] = acc ? old[i] + dx : dx;
+            dzs[i] = dz;
           }
         }
         __stcs(reinterpret_cast<float4 *>(po + (size_t)r * rs), make_float4(o[0], o[1], o[2], o[3]));
+        if (DIR == 1 && pr) __stcs(reinterpret_cast<float4 *>(pr + (size_t)r * rs), make_float4(dzs[0], dzs[1], dzs[2], dzs[3]));
       }
     }
     __syncthreads();      // this stage, the column arrays and the coefficients may be reused
@@ -367,7 +379,7 @@ static uint32_t seg_blocks_per_sm()
 
 // Geometry for direction `dir`, or false when this kernel does not apply: the shape is not a
 // "segments" shape, or a unit does not fit the shared memory of one cluster.
-static bool seg_geom(uint32_t dim0, uint32_t C, uint32_t N, int dir, SegGeom &g)
+static bool seg_geom(uint32_t dim0, uint32_t C, uint32_t N, int dir, bool extra, SegGeom &g)
 {
   const uint64_t row_stride = (uint64_t)C * dim0;
   if (row_stride % 4 != 0 || dim0 >= 512) return false;
@@ -378,7 +390,7 @@ static bool seg_geom(uint32_t dim0, uint32_t C, uint32_t N, int dir, SegGeom &g)
   while ((uint64_t)cb * dim0 < 128 && (uint64_t)(cb + q) * dim0 <= 4 * kSegThreads && cb + q <= 256) cb += q;
   if (cb >= C) cb = C;
   if ((uint64_t)cb * dim0 > 4 * kSegThreads || (cb * dim0) % 4 != 0) return false;
-  const uint32_t L = cb * dim0, tensors = dir == 1 ? 2 : 1;
+  const uint32_t L = cb * dim0, tensors = (dir == 1 ? 2u : 1u) + (extra ? 1u : 0u);
   const uint32_t per_block = (228u * 1024u) / seg_blocks_per_sm() - 1024u;       // what one of k co-resident blocks may use
   const uint32_t budget = per_block > 227u * 1024u ? 227u * 1024u : per_block;
   g.cb = cb; g.units = ceil_div_u32(C, cb);
@@ -396,7 +408,8 @@ static bool seg_geom(uint32_t dim0, uint32_t C, uint32_t N, int dir, SegGeom &g)
   g.cluster = cl;
   g.rows = ceil_div_u32(N, cl);
   const uint32_t slice = (uint32_t)align_up_u64((uint64_t)g.rows * L * 4, 128);
-  g.off_dy = slice;                         // within a stage: x, then dy
+  g.off_dy = slice;                         // within a stage: x, then dy (backward), then the extra tensor
+  g.off_e = (dir == 1 ? 2u : 1u) * slice;
   g.stage_bytes = tensors * slice;
   g.smem_bytes = g.off_stage + g.stages * g.stage_bytes;
   return g.smem_bytes <= budget;
@@ -405,7 +418,8 @@ static bool seg_geom(uint32_t dim0, uint32_t C, uint32_t N, int dir, SegGeom &g)
 bool segres_applies(const FusedArgs &a, int dir, bool aligned)
 {
   SegGeom g;
-  return aligned && a.mode == MODE_FUSED && seg_geom(a.plan.dim0, a.plan.C, a.plan.N, dir, g);
+  const bool extra = (dir == 0 ? a.res : a.ymask) != nullptr;
+  return aligned && a.mode == MODE_FUSED && seg_geom(a.plan.dim0, a.plan.C, a.plan.N, dir, extra, g);
 }
 
 // Launches the segments kernel for a prepared call.  ANODE_E_LAUNCH when the device refuses the
@@ -413,7 +427,7 @@ bool segres_applies(const FusedArgs &a, int dir, bool aligned)
 int launch_segres(FusedArgs &a, int dir, cudaStream_t stream)
 {
   SegGeom g;
-  if (!seg_geom(a.plan.dim0, a.plan.C, a.plan.N, dir, g)) return ANODE_E_LAUNCH;
+  if (!seg_geom(a.plan.dim0, a.plan.C, a.plan.N, dir, (dir == 0 ? a.res : a.ymask) != nullptr, g)) return ANODE_E_LAUNCH;
   auto kernel = dir == 0 ? bn_segres_kernel<0> : bn_segres_kernel<1>;
   static std::mutex mu;
   static std::map<std::pair<const void *, uint64_t>, int> fit_cache;     // (kernel, smem | cluster) -> clusters resident at once
@@ -464,7 +478,7 @@ extern "C" int anode_gpu_batch_norm_segres_geometry(uint32_t dim0, uint32_t dim1
   using namespace anode_b200;
   if (!out || check_dims(dim0, dim1, dim2)) return ANODE_E_DIMS;
   SegGeom g{};
-  const bool ok = seg_geom(dim0, dim1, dim2, dir, g);
+  const bool ok = seg_geom(dim0, dim1, dim2, dir, false, g);
   out[0] = ok ? 1u : 0u; out[1] = g.cb; out[2] = g.cluster; out[3] = g.rows; out[4] = g.units; out[5] = g.smem_bytes;
   return ANODE_OK;
 }

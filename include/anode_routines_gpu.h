@@ -246,7 +246,8 @@ int anode_gpu_batch_norm_act_fused_bwd_3d1_packed_f32(
  * normalized branch, then positive_clip).  Backward: the mask is taken from the saved output y (as
  * the reference's positive_clip adjoint does, flat_map.cu:187-194); dresidual = dy*mask is the
  * gradient of the shortcut (may be NULL, may alias dy); dx, dgamma, dbeta as in the calls above.
- * Served by the plain kernel (12 / 20 algorithmic bytes per element forward / backward). */
+ * Served by the cluster kernel for short rows and by the plain kernel otherwise (12 / 20 algorithmic
+ * bytes per element forward / backward). */
 int anode_gpu_batch_norm_add_act_fused_fwd_3d1_packed_f32(
     uint32_t dim0, uint32_t dim1, uint32_t dim2,
     float epsilon, float avg_rate, float neg_slope,
