@@ -84,7 +84,6 @@ static RingGeom ring_geom(const Plan &p, int dir, uint32_t slots, uint32_t slot_
   g.res_stride = p.cb > cwarps ? p.cb : cwarps;   // regime R: one partial per consumer warp
   g.off_res = off;  off += (uint32_t)align_up_u64((uint64_t)kResQ * g.res_stride * 16, 128);
   g.off_coef = off; off += (uint32_t)align_up_u64((uint64_t)kCoefQ * p.cb * 32, 128);
-  g.off_seg = off;  if (p.regime == 1) off += 2 * kSegMaxFloats * 4;
   g.off_slots = off;
   g.slot_stride = (uint32_t)align_up_u64((uint64_t)slot_floats * 4 * (dir == 1 ? 2 : 1) + (dir == 1 ? (uint64_t)p.cb * 16 : 0), 128);
   g.smem_bytes = off + slots * g.slot_stride;
@@ -99,12 +98,12 @@ bool ring_plan_for(uint32_t dim0, uint32_t C, uint32_t N, bool aligned, int dir,
   if (!t.ring || !aligned) return false;
   uint32_t slot_floats = dir == 0 ? t.ring_floats_fwd : t.ring_floats_bwd;
   slot_floats = (slot_floats / 4) * 4;
-  if (slot_floats < kSegMaxFloats) slot_floats = kSegMaxFloats;   // a regime-S segment must fit
+  if (slot_floats < 1024) slot_floats = 1024;
   uint32_t slots = dir == 0 ? t.ring_slots : t.ring_slots_bwd;
   slots = slots < 2 ? 2 : (slots > kMaxSlots ? kMaxSlots : slots);
   uint32_t bps = t.ring_blocks_per_sm ? t.ring_blocks_per_sm : 1;
   p = make_plan(dim0, C, N, true, sm_count() * bps, slot_floats, t.slack_steps);
-  // regime S (short rows) stays on the plain kernel: its per-unit merge is too slow in one warp
+  // short rows (regime S) belong to the cluster kernel or the plain kernel
   if (p.vec != 4 || p.regime != 0) return false;
   // a tile must fit one slot: rows * len <= slot_floats
   const uint64_t tile_max = (uint64_t)p.rows_per_tile * p.piece_len;

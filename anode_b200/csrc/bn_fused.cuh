@@ -719,7 +719,7 @@ constexpr uint32_t kCoefQ = 4;         // coefficient mailbox depth
 constexpr uint32_t kMaxSlots = 8;
 constexpr uint32_t kRingCtlBytes = 1024;   // room reserved for the kernel's barrier block (RingCtl)
 struct RingGeom {
-  uint32_t slots, slot_floats, slot_stride, res_stride, off_res, off_coef, off_seg, off_slots, smem_bytes;
+  uint32_t slots, slot_floats, slot_stride, res_stride, off_res, off_coef, off_slots, smem_bytes;
 };
 
 }  // namespace anode_b200
