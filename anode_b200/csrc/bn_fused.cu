@@ -217,6 +217,8 @@ int launch_best(FusedArgs &a, int dir, bool aligned, cudaStream_t stream)
     if (tunables().segres && segres_applies(a, dir, aligned) && launch_segres(a, dir, stream) == ANODE_OK) return ANODE_OK;
     return launch_pipeline(a, dir, stream);
   }
+  // short rows, and channels small enough to sit in a few blocks' shared memory: the cluster kernel
+  if (tunables().segres && segres_preferred(a, dir, aligned) && launch_segres(a, dir, stream) == ANODE_OK) return ANODE_OK;
   if (ring_plan_for(a.plan.dim0, a.plan.C, a.plan.N, aligned, dir, rp, g) && rp.ws_bytes <= a.ws_capacity) {
     a.plan = rp;
     return launch_ring(a, g, dir, stream);
@@ -492,9 +494,10 @@ extern "C" int anode_gpu_batch_norm_fused_kernel_kind(uint32_t dim0, uint32_t di
 {
   if (check_dims(dim0, dim1, dim2)) return ANODE_E_DIMS;
   Plan rp; RingGeom g;
-  if (ring_plan_for(dim0, dim1, dim2, true, dir, rp, g)) return 1;
   FusedArgs a{};
   a.plan.dim0 = dim0; a.plan.C = dim1; a.plan.N = dim2; a.mode = MODE_FUSED;
+  if (tunables().segres && segres_preferred(a, dir, true)) return 2;
+  if (ring_plan_for(dim0, dim1, dim2, true, dir, rp, g)) return 1;
   if (tunables().segres && segres_applies(a, dir, true)) return 2;
   return 0;
 }

@@ -48,6 +48,7 @@ int launch_best(FusedArgs &a, int dir, bool aligned, cudaStream_t stream);
 bool ring_applies(const FusedArgs &a, int dir, bool aligned);
 // the cluster kernel for short rows (bn_segres.cu)
 bool segres_applies(const FusedArgs &a, int dir, bool aligned);
+bool segres_preferred(const FusedArgs &a, int dir, bool aligned);      // take it even where the tiled kernel applies
 int launch_segres(FusedArgs &a, int dir, cudaStream_t stream);
 uint64_t workspace_part_bytes(uint32_t dim0, uint32_t C, uint32_t N);
 uint64_t control_region_bytes(uint32_t dim0, uint32_t C, uint32_t N, bool aligned);

@@ -382,8 +382,8 @@ static uint32_t seg_blocks_per_sm()
 static bool seg_geom(uint32_t dim0, uint32_t C, uint32_t N, int dir, bool extra, SegGeom &g)
 {
   const uint64_t row_stride = (uint64_t)C * dim0;
-  if (row_stride % 4 != 0 || dim0 >= 512) return false;
-  if (dim0 >= 256 && dim0 % 4 == 0) return false;              // long aligned rows: the tiled kernels' case
+  if (row_stride % 4 != 0 || dim0 > 4 * kSegThreads) return false;      // a row must fit one column per thread
+  if (dim0 >= 512 && dim0 % 4 != 0) return false;              // long unaligned rows: the plain kernel's case
   uint32_t q = 4; if (dim0 % 2 == 0) q = 2; if (dim0 % 4 == 0) q = 1;      // cb*dim0 must be a multiple of 4
   // the smallest cb that gives runs of at least 512 bytes, within 256 float4 columns and 256 channels
   uint32_t cb = q;
@@ -413,6 +413,21 @@ static bool seg_geom(uint32_t dim0, uint32_t C, uint32_t N, int dir, bool extra,
   g.stage_bytes = tensors * slice;
   g.smem_bytes = g.off_stage + g.stages * g.stage_bytes;
   return g.smem_bytes <= budget;
+}
+
+// Long aligned rows (256 <= dim0, dim0 % 4 == 0) are also the tiled kernel's shapes.  The cluster
+// kernel takes them when a channel is small enough to sit in a few blocks' shared memory: then its
+// latency (one short pass, no pipeline to fill and drain) beats the tiled kernel's throughput.
+bool segres_preferred(const FusedArgs &a, int dir, bool aligned)
+{
+  if (!segres_applies(a, dir, aligned)) return false;
+  const uint32_t dim0 = a.plan.dim0;
+  if (dim0 < 256 || dim0 % 4 != 0) return true;                // short or unaligned rows: always
+  SegGeom g;
+  const bool extra = (dir == 0 ? a.res : a.ymask) != nullptr;
+  if (!seg_geom(dim0, a.plan.C, a.plan.N, dir, extra, g)) return false;
+  static const uint32_t max_cluster = seg_env("ANODE_B200_SEG_LONG_CLUSTER", 0, 16, 4);      // 0: never
+  return g.cluster <= max_cluster;
 }
 
 bool segres_applies(const FusedArgs &a, int dir, bool aligned)

@@ -135,6 +135,9 @@ def test_cluster_kernel_geometry_invariants():
     # long aligned rows belong to the tiled kernel, odd strides to the plain one
     assert lib.anode_gpu_batch_norm_fused_kernel_kind(3136, 256, 2048, 0) == 1
     assert lib.anode_gpu_batch_norm_fused_kernel_kind(117, 5, 3, 1) == 0
+    # long aligned rows whose channel fits a few blocks' shared memory: the cluster kernel takes them
+    assert lib.anode_gpu_batch_norm_fused_kernel_kind(784, 64, 32, 0) == 2
+    assert lib.anode_gpu_batch_norm_fused_kernel_kind(784, 2048, 1024, 0) == 1
 
 
 def test_host_step_block_count_and_staging_size():
