@@ -1,6 +1,8 @@
-// Fused batch-norm (+ReLU) for short rows: the "segments" shapes (dim0 < 256 or rows that are not
-// 16-byte aligned one by one, e.g. [N, 2048, 7, 7]), where a channel's data is N short runs far
-// apart and the tiled kernels spend more time on bookkeeping than on data.
+// Fused batch-norm (+activation) for short rows: the "segments" shapes (dim0 < 256 or rows that are
+// not 16-byte aligned one by one, e.g. [N, 2048, 7, 7]), where a channel's data is N short runs far
+// apart and the tiled kernels spend more time on bookkeeping than on data; also rows of up to 1024
+// floats (e.g. 28 x 28) when a channel is small enough to sit in a few blocks' shared memory, and
+// the residual-block epilogue on those shapes (a third tensor in the slice).
 //
 // Decomposition: a unit is a block of cb channels, i.e. per sample one contiguous, 16-byte aligned
 // run of L = cb*dim0 floats.  A thread-block CLUSTER of CL blocks owns one unit; block r of the
