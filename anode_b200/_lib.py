@@ -61,6 +61,7 @@ SIGNATURES = {
         (c_int, _D + [f32, c_int] + [vp] * 11 + [vp, size_t] + _T),
     "anode_gpu_batch_norm_relu_fused_fwd_static_3d1_packed_f32":
         (c_int, _D + [f32, f32, c_int] + [vp] * 8 + _T),
+    "anode_gpu_batch_norm_fused_static_status": (c_int, [vp, ctypes.POINTER(u32)]),
     "anode_gpu_batch_norm_host_step_staging_bytes": (size_t, _D + [u32]),
     "anode_gpu_batch_norm_host_step_blocks": (u32, _D + [u32]),
     "anode_gpu_batch_norm_relu_fused_step_host_3d1_packed_f32":
@@ -71,6 +72,7 @@ SIGNATURES = {
     "anode_gpu_sync_get_unique_id": (c_int, [vp]),
     "anode_gpu_sync_comm_create": (c_int, [vp, c_int, c_int, ctypes.POINTER(vp)]),
     "anode_gpu_sync_comm_destroy": (c_int, [vp]),
+    "anode_gpu_sync_comm_create_exchange_only": (c_int, [c_int, c_int, ctypes.POINTER(vp)]),
     "anode_gpu_sync_allreduce_sum_f32": (c_int, [vp, vp, size_t, vp]),
     "anode_gpu_sync_exchange_bytes": (size_t, [u32, c_int]),
     "anode_gpu_sync_comm_attach_exchange": (c_int, [vp, ctypes.POINTER(vp), u32]),
@@ -84,6 +86,11 @@ SIGNATURES = {
         (c_int, _D + [c_int, u32, u32, u32, u32, u32, ctypes.POINTER(ctypes.c_uint64)]),
     "anode_gpu_batch_norm_segres_geometry": (c_int, _D + [c_int, ctypes.POINTER(u32)]),
     "anode_gpu_batch_norm_fused_kernel_kind": (c_int, _D + [c_int]),
+    "anode_gpu_batch_norm_fused_set_wait_limit_ms": (c_int, [u32]),
+    "anode_gpu_batch_norm_fused_set_kernel": (c_int, [c_int]),
+    "anode_gpu_batch_norm_resident_plan": (c_int, _D + [u32, ctypes.POINTER(u32)]),
+    "anode_gpu_batch_norm_resident_schedule":
+        (ctypes.c_longlong, _D + [u32, u32, ctypes.POINTER(u32), ctypes.c_uint64]),
     "anode_gpu_batch_norm_fused_plan_tile":
         (c_int, _D + [c_int, u32, u32, u32, ctypes.POINTER(ctypes.c_uint64)]),
 }

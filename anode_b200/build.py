@@ -11,8 +11,8 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libanode_routines_gpu.so")
-SOURCES = ["bn_fused.cu", "bn_legacy.cu", "bn_sync.cu", "bn_static.cu", "bn_hoststep.cu", "bn_segres.cu", "bn_infer.cu"]
-HEADERS = ["bn_plan.h", "bn_device.cuh", "bn_fused.cuh", "bn_ring.cuh", "bn_host.h", "bn_sync.h",
+SOURCES = ["bn_fused.cu", "bn_legacy.cu", "bn_sync.cu", "bn_static.cu", "bn_hoststep.cu", "bn_segres.cu", "bn_infer.cu", "bn_resident.cu", "bn_resident_diag.cpp"]
+HEADERS = ["bn_plan.h", "bn_device.cuh", "bn_fused.cuh", "bn_ring.cuh", "bn_resident_plan.h", "bn_host.h", "bn_sync.h",
            os.path.join("..", "..", "include", "anode_routines_gpu.h")]
 
 NVCC_FLAGS = [
@@ -55,7 +55,7 @@ def build_library(force=False, verbose=False):
     objs = []
     procs = []
     for s in _sources():
-        obj = os.path.join(CSRC, s[:-3] + ".o")
+        obj = os.path.join(CSRC, os.path.splitext(s)[0] + ".o")
         cmd = [nvcc] + NVCC_FLAGS + ["-I", _nccl_include(), "-c", os.path.join(CSRC, s), "-o", obj]
         if verbose:
             cmd.insert(1, "-Xptxas=-v")

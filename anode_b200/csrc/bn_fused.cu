@@ -15,33 +15,28 @@
 
 namespace anode_b200 {
 
-// ---- tunables (read once; environment overrides exist for experiments only) --------------
-static uint32_t env_u32(const char *name, uint32_t dflt)
-{
-  const char *s = getenv(name);
-  if (!s || !*s) return dflt;
-  const long v = strtol(s, nullptr, 10);
-  return v >= 0 ? (uint32_t)v : dflt;
-}
-
+// ---- planner constants, from sweeps on B200 -------------------------------------------------------
 const Tunables &tunables()
 {
   static const Tunables t = {
-      env_u32("ANODE_B200_TILE_FLOATS", 32768),
-      env_u32("ANODE_B200_SLACK_STEPS", 2),
-      env_u32("ANODE_B200_BLOCKS_PER_SM", 4),
-      env_u32("ANODE_B200_RING", 1),
-      env_u32("ANODE_B200_RING_SLOTS", 3),
-      env_u32("ANODE_B200_RING_SLOTS_BWD", 4),
-      env_u32("ANODE_B200_RING_FLOATS_FWD", 16384),
-      env_u32("ANODE_B200_RING_FLOATS_BWD", 8192),
-      env_u32("ANODE_B200_RING_BLOCKS_PER_SM", 1),
-      env_u32("ANODE_B200_RING_WARPS_FWD", 8),
-      env_u32("ANODE_B200_RING_WARPS_BWD", 16),
-      env_u32("ANODE_B200_SEGRES", 1),
+      32768,    // tile_floats
+      2,        // slack_steps
+      4,        // blocks_per_sm
+      3,        // ring_slots
+      4,        // ring_slots_bwd
+      16384,    // ring_floats_fwd
+      8192,     // ring_floats_bwd
+      1,        // ring_blocks_per_sm
+      8,        // ring_warps_fwd
+      16,       // ring_warps_bwd
   };
   return t;
 }
+
+// Which kernel serves the fused calls: ANODE_KERNEL_AUTO picks by shape; any other value is tried first
+// where that kernel applies (set by tests and measurements, process-wide).
+static std::atomic<int> g_kernel_choice{ANODE_KERNEL_AUTO};
+int kernel_choice() { return g_kernel_choice.load(std::memory_order_relaxed); }
 
 uint32_t sm_count()
 {
@@ -95,7 +90,7 @@ static RingGeom ring_geom(const Plan &p, int dir, uint32_t slots, uint32_t slot_
 bool ring_plan_for(uint32_t dim0, uint32_t C, uint32_t N, bool aligned, int dir, Plan &p, RingGeom &g)
 {
   const Tunables &t = tunables();
-  if (!t.ring || !aligned) return false;
+  if (!aligned) return false;
   uint32_t slot_floats = dir == 0 ? t.ring_floats_fwd : t.ring_floats_bwd;
   slot_floats = (slot_floats / 4) * 4;
   if (slot_floats < 1024) slot_floats = 1024;
@@ -173,7 +168,9 @@ int launch_ring(FusedArgs &a, const RingGeom &g, int dir, cudaStream_t stream)
 // direction's kernels keep state in their part from launch to launch (which partial buffer is
 // current, words waiting to be cleared), laid out by that direction's own tile plan, so forward
 // and backward launches must not share one.  The status word is the first word of the whole.
-uint64_t workspace_part_bytes(uint32_t dim0, uint32_t C, uint32_t N)
+// Bytes of a part taken by the tile-plan kernels (plain, warp-specialised, cluster); the records of the
+// slice-resident kernel follow behind them.
+static uint64_t tiled_part_bytes(uint32_t dim0, uint32_t C, uint32_t N)
 {
   // the plan depends on pointer alignment, which is not known yet: cover both cases
   const Plan a = plan_for(dim0, C, N, true), b = plan_for(dim0, C, N, false);
@@ -182,10 +179,12 @@ uint64_t workspace_part_bytes(uint32_t dim0, uint32_t C, uint32_t N)
     Plan rp; RingGeom g;
     if (ring_plan_for(dim0, C, N, true, dir, rp, g) && rp.ws_bytes > need) need = rp.ws_bytes;
   }
-#ifdef ANODE_RING_PROFILE
-  need += 1u << 20;     // room for the per-block cycle counters
-#endif
   return align_up_u64(need, 256);
+}
+
+uint64_t workspace_part_bytes(uint32_t dim0, uint32_t C, uint32_t N)
+{
+  return align_up_u64(tiled_part_bytes(dim0, C, N) + resident_ws_bytes(dim0, C, N), 256);
 }
 
 // Bytes at the start of a workspace that hold progress counters, flags and records, i.e. what has
@@ -197,6 +196,9 @@ uint64_t control_region_bytes(uint32_t dim0, uint32_t C, uint32_t N, bool aligne
     Plan rp; RingGeom g;
     if (ring_plan_for(dim0, C, N, aligned, dir, rp, g) && rp.off_part > n) n = rp.off_part;
   }
+  // the slice-resident kernel's records validate themselves against the launch counter in the header,
+  // which the clearing resets: they have to go too
+  if (aligned && resident_ws_bytes(dim0, C, N)) n = workspace_part_bytes(dim0, C, N);
   return n;
 }
 
@@ -207,26 +209,57 @@ bool ring_applies(const FusedArgs &a, int dir, bool aligned)
   return ring_plan_for(a.plan.dim0, a.plan.C, a.plan.N, aligned, dir, rp, g) && rp.ws_bytes <= a.ws_capacity;
 }
 
-// Launches direction `dir` of a prepared call with the best kernel that applies.
-int launch_best(FusedArgs &a, int dir, bool aligned, cudaStream_t stream)
+// Which kernel launch_best takes for a prepared call: ANODE_KERNEL_* (never AUTO), or -1 when none can
+// (a synchronized call in fused mode on a shape only the plain kernel takes: it has no exchange).
+int pick_kernel_kind(const FusedArgs &a, int dir, bool aligned)
 {
+  const bool extra = a.res || a.ymask || a.dres;        // residual epilogue
+  const bool plain_ok = !(a.mode == MODE_FUSED && a.world > 1);
   Plan rp; RingGeom g;
-  if (a.res || a.ymask || a.dres) {
-    // the residual epilogue exists in the cluster kernel (short rows) and in the plain kernel
-    if (a.mode == MODE_FUSED && a.world > 1) return ANODE_E_LAUNCH;
-    if (tunables().segres && segres_applies(a, dir, aligned) && launch_segres(a, dir, stream) == ANODE_OK) return ANODE_OK;
-    return launch_pipeline(a, dir, stream);
+  const bool tiled_ok = !extra && ring_plan_for(a.plan.dim0, a.plan.C, a.plan.N, aligned, dir, rp, g) && rp.ws_bytes <= a.ws_capacity;
+  switch (kernel_choice()) {
+    case ANODE_KERNEL_TILED: if (tiled_ok) return ANODE_KERNEL_TILED; break;
+    case ANODE_KERNEL_CLUSTER: if (segres_applies(a, dir, aligned)) return ANODE_KERNEL_CLUSTER; break;
+    case ANODE_KERNEL_RESIDENT: if (resident_applies(a, dir, aligned)) return ANODE_KERNEL_RESIDENT; break;
+    case ANODE_KERNEL_PLAIN: if (plain_ok) return ANODE_KERNEL_PLAIN; break;
+    default: break;
+  }
+  if (extra) {
+    // short rows: the cluster kernel; long rows: the slice-resident kernel; the rest: the plain kernel
+    if (segres_applies(a, dir, aligned)) return ANODE_KERNEL_CLUSTER;
+    if (resident_applies(a, dir, aligned)) return ANODE_KERNEL_RESIDENT;
+    return plain_ok ? ANODE_KERNEL_PLAIN : -1;
   }
   // short rows, and channels small enough to sit in a few blocks' shared memory: the cluster kernel
-  if (tunables().segres && segres_preferred(a, dir, aligned) && launch_segres(a, dir, stream) == ANODE_OK) return ANODE_OK;
-  if (ring_plan_for(a.plan.dim0, a.plan.C, a.plan.N, aligned, dir, rp, g) && rp.ws_bytes <= a.ws_capacity) {
+  if (segres_preferred(a, dir, aligned)) return ANODE_KERNEL_CLUSTER;
+  if (tiled_ok) return ANODE_KERNEL_TILED;
+  if (segres_applies(a, dir, aligned)) return ANODE_KERNEL_CLUSTER;
+  if (plain_ok) return ANODE_KERNEL_PLAIN;
+  return resident_applies(a, dir, aligned) ? ANODE_KERNEL_RESIDENT : -1;
+}
+
+// Launches direction `dir` of a prepared call with the kernel pick_kernel_kind names.  A cluster launch
+// the device refuses falls back to the next kernel that applies.
+int launch_best(FusedArgs &a, int dir, bool aligned, cudaStream_t stream)
+{
+  int kind = pick_kernel_kind(a, dir, aligned);
+  if (kind == ANODE_KERNEL_CLUSTER) {
+    if (launch_segres(a, dir, stream) == ANODE_OK) return ANODE_OK;
+    const bool extra = a.res || a.ymask || a.dres;
+    Plan rp; RingGeom g;
+    if (!extra && ring_plan_for(a.plan.dim0, a.plan.C, a.plan.N, aligned, dir, rp, g) && rp.ws_bytes <= a.ws_capacity) kind = ANODE_KERNEL_TILED;
+    else if (resident_applies(a, dir, aligned)) kind = ANODE_KERNEL_RESIDENT;
+    else kind = (a.mode == MODE_FUSED && a.world > 1) ? -1 : ANODE_KERNEL_PLAIN;
+  }
+  if (kind == ANODE_KERNEL_TILED) {
+    Plan rp; RingGeom g;
+    if (!ring_plan_for(a.plan.dim0, a.plan.C, a.plan.N, aligned, dir, rp, g)) return ANODE_E_LAUNCH;
     a.plan = rp;
     return launch_ring(a, g, dir, stream);
   }
-  if (tunables().segres && segres_applies(a, dir, aligned) && launch_segres(a, dir, stream) == ANODE_OK) return ANODE_OK;
-  // the plain kernel has no cross-GPU exchange: a synchronized call in fused mode must not end up here
-  if (a.mode == MODE_FUSED && a.world > 1) return ANODE_E_LAUNCH;
-  return launch_pipeline(a, dir, stream);
+  if (kind == ANODE_KERNEL_RESIDENT) return launch_resident(a, dir, tiled_part_bytes(a.plan.dim0, a.plan.C, a.plan.N), stream);
+  if (kind == ANODE_KERNEL_PLAIN) return launch_pipeline(a, dir, stream);
+  return ANODE_E_LAUNCH;
 }
 
 int check_dims(uint32_t dim0, uint32_t dim1, uint32_t dim2)
@@ -307,6 +340,7 @@ int prepare_fwd(FusedArgs &a, uint32_t dim0, uint32_t dim1, uint32_t dim2, float
   a.epsilon = epsilon; a.avg_rate = avg_rate; a.relu = relu ? 1u : 0u; a.neg_slope = relu ? 0.0f : 1.0f;
   a.mode = MODE_FUSED;
   a.count_total = (double)dim0 * (double)dim2;
+  a.wait_cycles = wait_limit_cycles();
   return ANODE_OK;
 }
 
@@ -331,6 +365,7 @@ int prepare_bwd(FusedArgs &a, uint32_t dim0, uint32_t dim1, uint32_t dim2, int r
   a.relu = relu ? 1u : 0u; a.neg_slope = relu ? 0.0f : 1.0f; a.accumulate = accumulate ? 1u : 0u;
   a.mode = MODE_FUSED;
   a.count_total = (double)dim0 * (double)dim2;
+  a.wait_cycles = wait_limit_cycles();
   return ANODE_OK;
 }
 
@@ -488,18 +523,23 @@ extern "C" int anode_gpu_online_average_f32(uint32_t len, float rate, const floa
   return ANODE_OK;
 }
 
-// Which kernel serves direction `dir` of a [dim0, dim1, dim2] call with 16-byte aligned tensors on
-// one GPU: 1 = warp-specialised tiled kernel, 2 = cluster kernel for short rows, 0 = plain kernel.
+// Which kernel serves direction `dir` of a plain [dim0, dim1, dim2] call with 16-byte aligned tensors on
+// one GPU: an ANODE_KERNEL_* value.
 extern "C" int anode_gpu_batch_norm_fused_kernel_kind(uint32_t dim0, uint32_t dim1, uint32_t dim2, int dir)
 {
   if (check_dims(dim0, dim1, dim2)) return ANODE_E_DIMS;
-  Plan rp; RingGeom g;
   FusedArgs a{};
-  a.plan.dim0 = dim0; a.plan.C = dim1; a.plan.N = dim2; a.mode = MODE_FUSED;
-  if (tunables().segres && segres_preferred(a, dir, true)) return 2;
-  if (ring_plan_for(dim0, dim1, dim2, true, dir, rp, g)) return 1;
-  if (tunables().segres && segres_applies(a, dir, true)) return 2;
-  return 0;
+  a.plan = plan_for(dim0, dim1, dim2, true);
+  a.mode = MODE_FUSED;
+  a.ws_capacity = workspace_part_bytes(dim0, dim1, dim2);
+  return pick_kernel_kind(a, dir, true);
+}
+
+extern "C" int anode_gpu_batch_norm_fused_set_kernel(int kernel)
+{
+  if (kernel < ANODE_KERNEL_AUTO || kernel > ANODE_KERNEL_PLAIN) return ANODE_E_DIMS;
+  g_kernel_choice.store(kernel, std::memory_order_relaxed);
+  return ANODE_OK;
 }
 
 // ---- diagnostics: the tile plan, for tests of the index arithmetic (no GPU needed) ----------

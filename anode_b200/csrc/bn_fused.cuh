@@ -51,6 +51,7 @@ struct FusedArgs {
   // mapped into this process (xchg[rank] is local memory); see bn_ring.cuh
   uint32_t rank, world, epoch, xchg_channels;
   unsigned long long *xchg[8];
+  long long wait_cycles;   // bound of every in-kernel wait, in SM clock cycles
 };
 
 // 1/sqrt(v) as every kernel here computes it (IEEE divide and square root), so that the
@@ -115,7 +116,8 @@ __device__ __forceinline__ size_t vec_off(const TileRange &tr, uint32_t per_row,
 __device__ __forceinline__ void finish_channel_fwd(const FusedArgs &a, uint32_t c, double n, double mean, double m2)
 {
   if (a.mode == MODE_STATS) {
-    __stcg(ws_f4(a, a.plan.off_local) + c, make_float4((float)n, (float)mean, (float)m2, 0.f));
+    // the count travels as an exact integer in the first word (a float would round counts above 2^24)
+    __stcg(ws_f4(a, a.plan.off_local) + c, make_float4(__uint_as_float((uint32_t)n), (float)mean, (float)m2, 0.f));
     return;
   }
   const float mf = (float)mean;

@@ -18,7 +18,6 @@ struct Tunables {
   uint32_t tile_floats;     // target floats per tile
   uint32_t slack_steps;     // extra lookahead steps beyond the minimum
   uint32_t blocks_per_sm;   // persistent blocks planned per SM
-  uint32_t ring;            // 1: use the warp-specialised kernel where it applies
   uint32_t ring_slots;      // shared-memory slots per block (forward)
   uint32_t ring_slots_bwd;  // shared-memory slots per block (backward; a slot holds x and dy)
   uint32_t ring_floats_fwd; // floats per slot (forward: x)
@@ -26,7 +25,6 @@ struct Tunables {
   uint32_t ring_blocks_per_sm;
   uint32_t ring_warps_fwd;  // consumer warps of the forward kernel (8 or 16)
   uint32_t ring_warps_bwd;  // consumer warps of the backward kernel (8 or 16)
-  uint32_t segres;          // 1: use the cluster kernel for short rows where it applies
 };
 const Tunables &tunables();
 
@@ -43,14 +41,21 @@ int prepare_bwd(FusedArgs &a, uint32_t dim0, uint32_t dim1, uint32_t dim2, int r
                 const float *dy, const float *x, const float *mean, const float *var, const float *gamma,
                 const float *beta, float *dx, float *dgamma, float *dbeta, void *ws, size_t ws_bytes);
 int launch_pipeline(FusedArgs &a, int dir, cudaStream_t stream);
-// picks the warp-specialised kernel where it applies, the plain one otherwise
+// the kernel that serves a prepared call (ANODE_KERNEL_*, -1 for none), and its launch
+int pick_kernel_kind(const FusedArgs &a, int dir, bool aligned);
 int launch_best(FusedArgs &a, int dir, bool aligned, cudaStream_t stream);
+int kernel_choice();
 bool ring_applies(const FusedArgs &a, int dir, bool aligned);
 // the cluster kernel for short rows (bn_segres.cu)
 bool segres_applies(const FusedArgs &a, int dir, bool aligned);
 bool segres_preferred(const FusedArgs &a, int dir, bool aligned);      // take it even where the tiled kernel applies
 int launch_segres(FusedArgs &a, int dir, cudaStream_t stream);
 uint64_t workspace_part_bytes(uint32_t dim0, uint32_t C, uint32_t N);
+// the slice-resident kernel (bn_resident.cu)
+bool resident_applies(const FusedArgs &a, int dir, bool aligned);
+uint64_t resident_ws_bytes(uint32_t dim0, uint32_t C, uint32_t N);
+int launch_resident(FusedArgs &a, int dir, uint64_t ws_off, cudaStream_t stream);
+long long wait_limit_cycles();
 uint64_t control_region_bytes(uint32_t dim0, uint32_t C, uint32_t N, bool aligned);
 
 }  // namespace anode_b200

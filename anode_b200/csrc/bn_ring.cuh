@@ -580,14 +580,15 @@ __device__ __forceinline__ bool pull_merge_unit(const FusedArgs &a, RingCtl *ctl
     const size_t slot = (((size_t)par * a.world) * a.xchg_channels + u) * 4;      // + src * xchg_channels * 4
     const size_t src_stride = (size_t)a.xchg_channels * 4;
     if (owner && lane < a.world) {
-      const float w0 = DIR == 0 ? (float)tot.n : (float)s1;
-      const float w1 = DIR == 0 ? (float)tot.mean : (float)s2;
-      const float w2 = DIR == 0 ? (float)tot.m2 : 0.f;
+      // word 0 of a forward record is the element count as an exact integer (a float would round counts above 2^24)
+      const uint32_t w0 = DIR == 0 ? (uint32_t)tot.n : __float_as_uint((float)s1);
+      const uint32_t w1 = __float_as_uint(DIR == 0 ? (float)tot.mean : (float)s2);
+      const uint32_t w2 = __float_as_uint(DIR == 0 ? (float)tot.m2 : 0.f);
       unsigned long long *dst = a.xchg[lane] + slot + a.rank * src_stride;       // this rank's slot in peer `lane`
       const unsigned long long e = (unsigned long long)a.epoch << 32;
-      st_relaxed_sys_u64(dst + 0, e | __float_as_uint(w0));
-      st_relaxed_sys_u64(dst + 1, e | __float_as_uint(w1));
-      st_relaxed_sys_u64(dst + 2, e | __float_as_uint(w2));
+      st_relaxed_sys_u64(dst + 0, e | w0);
+      st_relaxed_sys_u64(dst + 1, e | w1);
+      st_relaxed_sys_u64(dst + 2, e | w2);
     }
     // lane r collects rank r's record from this GPU's own buffer
     const unsigned long long *mine = a.xchg[a.rank] + slot + (lane < a.world ? lane : 0) * src_stride;
@@ -603,14 +604,14 @@ __device__ __forceinline__ bool pull_merge_unit(const FusedArgs &a, RingCtl *ctl
       uint32_t stop = 0;
       if (lane == 0) {
         if (ctl->abort) stop = 1;
-        else if (clock64() - t0 > kWaitCycles) { atomicOr(status, ANODE_ST_WAIT_PEER); ctl->abort = 1; stop = 1; }
+        else if (clock64() - t0 > a.wait_cycles) { atomicOr(status, ANODE_ST_WAIT_PEER); ctl->abort = 1; stop = 1; }
       }
       if (__shfl_sync(0xffffffffu, stop, 0)) return false;
     }
     // merge in rank order (lane = rank; the shuffle tree is the same on every GPU, so all ranks
     // obtain bit-identical statistics)
     const bool live = lane < a.world;
-    const double f0 = live ? (double)__uint_as_float((uint32_t)v0) : 0.0;
+    const double f0 = live ? (DIR == 0 ? (double)(uint32_t)v0 : (double)__uint_as_float((uint32_t)v0)) : 0.0;
     const double f1 = live ? (double)__uint_as_float((uint32_t)v1) : 0.0;
     const double f2 = live ? (double)__uint_as_float((uint32_t)v2) : 0.0;
     if constexpr (DIR == 0) {

@@ -27,7 +27,6 @@
 // 314-336 (forward) and :181-206, 240-280, 354-376, 408-444, 476-515 (backward), with the ReLU of
 // routines_gpu/flat_map.cu:172-194 folded in.
 #include <cooperative_groups.h>
-#include <stdio.h>
 
 #include "bn_device.cuh"
 #include "bn_host.h"
@@ -67,7 +66,6 @@ __device__ __forceinline__ void st_sys_u64(unsigned long long *p, unsigned long 
 {
   asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
 }
-constexpr long long kSegWaitCycles = 3000000000ll;      // bound of the wait for a peer's record: about 1.5 s
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void cp_async_wait_but_one() { asm volatile("cp.async.wait_group 1;" ::: "memory"); }
 
@@ -262,15 +260,16 @@ __global__ void __launch_bounds__(kSegThreads) bn_segres_kernel(const FusedArgs 
         const size_t slot = ((((size_t)(a.epoch & 1u)) * a.world) * a.xchg_channels + c) * 4;
         const size_t src_stride = (size_t)a.xchg_channels * 4;
         if (rank == 0) {
-          float w0, w1, w2;
-          if (DIR == 0) { const double mean = t1 / t0; w0 = (float)t0; w1 = (float)mean; w2 = (float)fmax(t2 - t1 * mean, 0.0); }
-          else { w0 = (float)t1; w1 = (float)t2; w2 = 0.f; }
+          // word 0 of a forward record is the element count as an exact integer
+          uint32_t w0, w1, w2;
+          if (DIR == 0) { const double mean = t1 / t0; w0 = (uint32_t)t0; w1 = __float_as_uint((float)mean); w2 = __float_as_uint((float)fmax(t2 - t1 * mean, 0.0)); }
+          else { w0 = __float_as_uint((float)t1); w1 = __float_as_uint((float)t2); w2 = 0u; }
           const unsigned long long e = (unsigned long long)a.epoch << 32;
           for (uint32_t r = 0; r < a.world; ++r) {
             unsigned long long *dst = a.xchg[r] + slot + a.rank * src_stride;
-            st_sys_u64(dst + 0, e | __float_as_uint(w0));
-            st_sys_u64(dst + 1, e | __float_as_uint(w1));
-            st_sys_u64(dst + 2, e | __float_as_uint(w2));
+            st_sys_u64(dst + 0, e | w0);
+            st_sys_u64(dst + 1, e | w1);
+            st_sys_u64(dst + 2, e | w2);
           }
         }
         t0 = 0.0; t1 = 0.0; t2 = 0.0;
@@ -281,10 +280,11 @@ __global__ void __launch_bounds__(kSegThreads) bn_segres_kernel(const FusedArgs 
           for (;;) {
             v0 = ld_sys_u64(src + 0); v1 = ld_sys_u64(src + 1); v2 = ld_sys_u64(src + 2);
             if ((uint32_t)(v0 >> 32) == a.epoch && (uint32_t)(v1 >> 32) == a.epoch && (uint32_t)(v2 >> 32) == a.epoch) break;
-            if (clock64() - w_start > kSegWaitCycles) { atomicOr(a.status, ANODE_ST_WAIT_PEER); break; }   // give up, leave a mark
+            if (clock64() - w_start > a.wait_cycles) { atomicOr(a.status, ANODE_ST_WAIT_PEER); break; }   // give up, leave a mark
             __nanosleep(200);
           }
-          const double f0 = (double)__uint_as_float((uint32_t)v0), f1 = (double)__uint_as_float((uint32_t)v1);
+          const double f0 = DIR == 0 ? (double)(uint32_t)v0 : (double)__uint_as_float((uint32_t)v0);
+          const double f1 = (double)__uint_as_float((uint32_t)v1);
           const double f2 = (double)__uint_as_float((uint32_t)v2);
           if (DIR == 0) { t0 += f0; t1 = fma(f0, f1, t1); t2 += f2 + f0 * f1 * f1; }
           else { t1 += f0; t2 += f1; }
@@ -361,23 +361,12 @@ __global__ void __launch_bounds__(kSegThreads) bn_segres_kernel(const FusedArgs 
 
 // ---- host side -------------------------------------------------------------------------------
 
-// Two ways to overlap copies with arithmetic, chosen by environment for experiments:
-//   stages 1 (default): one unit per cluster and launch, two blocks share an SM;
-//   stages 2: persistent clusters, one block per SM holding two slices (the next unit's copies are
-//   in flight while the current one is worked on).  Measured slower: what limits this kernel is the
-//   chain of short dependent phases per unit, which co-resident blocks overlap better.
-static uint32_t seg_env(const char *name, uint32_t lo, uint32_t hi, uint32_t dflt)
-{
-  const char *e = getenv(name);
-  const long n = e ? strtol(e, nullptr, 10) : 0;
-  return (uint32_t)((e && n >= (long)lo && n <= (long)hi) ? n : dflt);
-}
-static uint32_t seg_stages() { static const uint32_t v = seg_env("ANODE_B200_SEG_STAGES", 1, 2, 1); return v; }
-static uint32_t seg_blocks_per_sm()
-{
-  static const uint32_t v = seg_env("ANODE_B200_SEG_BLOCKS_PER_SM", 1, 4, seg_stages() == 2 ? 1 : 2);
-  return v;
-}
+// One unit per cluster and launch; two blocks share an SM, so that one block's copies overlap the
+// other's arithmetic.  (A persistent variant with two slices per block was measured slower: what
+// limits this kernel is the chain of short dependent phases per unit, which co-resident blocks overlap
+// better.)
+constexpr uint32_t kSegBlocksPerSm = 2;
+constexpr uint32_t kSegLongRowCluster = 4;      // long aligned rows are taken when a channel fits this many blocks
 
 // Geometry for direction `dir`, or false when this kernel does not apply: the shape is not a
 // "segments" shape, or a unit does not fit the shared memory of one cluster.
@@ -393,7 +382,7 @@ static bool seg_geom(uint32_t dim0, uint32_t C, uint32_t N, int dir, bool extra,
   if (cb >= C) cb = C;
   if ((uint64_t)cb * dim0 > 4 * kSegThreads || (cb * dim0) % 4 != 0) return false;
   const uint32_t L = cb * dim0, tensors = (dir == 1 ? 2u : 1u) + (extra ? 1u : 0u);
-  const uint32_t per_block = (228u * 1024u) / seg_blocks_per_sm() - 1024u;       // what one of k co-resident blocks may use
+  const uint32_t per_block = (228u * 1024u) / kSegBlocksPerSm - 1024u;       // what one of k co-resident blocks may use
   const uint32_t budget = per_block > 227u * 1024u ? 227u * 1024u : per_block;
   g.cb = cb; g.units = ceil_div_u32(C, cb);
   g.off_col = 0;
@@ -401,7 +390,7 @@ static bool seg_geom(uint32_t dim0, uint32_t C, uint32_t N, int dir, bool extra,
   g.off_part = g.off_coef + (uint32_t)align_up_u64((uint64_t)cb * 32, 16);
   g.off_stage = g.off_part + (uint32_t)align_up_u64((uint64_t)2 * cb * 16, 128);
   // `stages` stages of `tensors` slices each; a slice is padded to 128 bytes
-  g.stages = seg_stages();
+  g.stages = 1;
   if (g.off_stage + (uint64_t)g.stages * tensors * ((uint64_t)L * 4 + 128) > budget) return false;
   const uint32_t rows_max = (uint32_t)(((budget - g.off_stage) / (g.stages * tensors) - 128) / (L * 4));
   uint32_t cl = 1;
@@ -428,8 +417,7 @@ bool segres_preferred(const FusedArgs &a, int dir, bool aligned)
   SegGeom g;
   const bool extra = (dir == 0 ? a.res : a.ymask) != nullptr;
   if (!seg_geom(dim0, a.plan.C, a.plan.N, dir, extra, g)) return false;
-  static const uint32_t max_cluster = seg_env("ANODE_B200_SEG_LONG_CLUSTER", 0, 16, 4);      // 0: never
-  return g.cluster <= max_cluster;
+  return g.cluster <= kSegLongRowCluster;
 }
 
 bool segres_applies(const FusedArgs &a, int dir, bool aligned)
@@ -475,9 +463,6 @@ int launch_segres(FusedArgs &a, int dir, cudaStream_t stream)
     }
     fit = it->second;
   }
-  if (getenv("ANODE_B200_SEG_DEBUG"))
-    fprintf(stderr, "segres dir=%d cb=%u cluster=%u rows=%u units=%u smem=%u resident clusters=%d\n", dir, g.cb, g.cluster,
-            g.rows, g.units, g.smem_bytes, fit);
   if (fit <= 0) return ANODE_E_LAUNCH;
   // two stages: as many clusters as are resident at once walk the units; one stage: a cluster per unit
   const uint32_t clusters = (g.stages == 2 && (uint32_t)fit < g.units) ? (uint32_t)fit : g.units;

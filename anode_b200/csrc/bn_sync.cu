@@ -52,7 +52,8 @@ static const NcclApi &nccl()
 }
 
 // ---- merge kernels: G records per channel -> global statistics and coefficients ---------------
-// gathered: [world][C] float4.  One thread per channel; every rank computes the same thing.
+// gathered: [world][C] float4; the first word of a forward record is the element count as an integer.
+// One thread per channel; every rank computes the same thing.
 __global__ void sync_merge_fwd_kernel(FusedArgs a, const float4 *gathered, uint32_t world)
 {
   const uint32_t c = blockIdx.x * blockDim.x + threadIdx.x;
@@ -60,14 +61,15 @@ __global__ void sync_merge_fwd_kernel(FusedArgs a, const float4 *gathered, uint3
   double sn = 0.0, sm = 0.0;
   for (uint32_t r = 0; r < world; ++r) {
     const float4 p = gathered[(size_t)r * a.plan.C + c];
-    sn += (double)p.x; sm += (double)p.x * (double)p.y;
+    const double n = (double)__float_as_uint(p.x);
+    sn += n; sm += n * (double)p.y;
   }
   const double mean = sm / sn;
   double sq = 0.0;
   for (uint32_t r = 0; r < world; ++r) {
     const float4 p = gathered[(size_t)r * a.plan.C + c];
     const double d = (double)p.y - mean;
-    sq += (double)p.z + (double)p.x * d * d;
+    sq += (double)p.z + (double)__float_as_uint(p.x) * d * d;
   }
   a.mode = MODE_APPLY;          // makes finish_channel_fwd write outputs and coefficients
   a.use_rec = 0;
@@ -88,26 +90,115 @@ __global__ void sync_merge_bwd_kernel(FusedArgs a, const float4 *gathered, uint3
   finish_channel_bwd(a, c, s1, s2);
 }
 
+// The exchange of the one-kernel form as a kernel of its own, for shapes none of the kernels with a
+// built-in exchange takes (scalar paths): same records, same buffers, same sequence numbers, so ranks
+// may mix the two forms freely.  One thread per channel: ship this GPU's record to every rank, collect
+// the ranks' records from this GPU's own buffer (bounded wait), merge in rank order.
+template <int DIR>
+__global__ void sync_exchange_kernel(FusedArgs a, const float4 *local)
+{
+  const uint32_t c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= a.plan.C) return;
+  const float4 mine = __ldcg(local + c);
+  const size_t slot = ((((size_t)(a.epoch & 1u)) * a.world) * a.xchg_channels + c) * 4;
+  const size_t src_stride = (size_t)a.xchg_channels * 4;
+  const unsigned long long e = (unsigned long long)a.epoch << 32;
+  for (uint32_t r = 0; r < a.world; ++r) {
+    unsigned long long *dst = a.xchg[r] + slot + a.rank * src_stride;
+    asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(dst + 0), "l"(e | __float_as_uint(mine.x)) : "memory");
+    asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(dst + 1), "l"(e | __float_as_uint(mine.y)) : "memory");
+    asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(dst + 2), "l"(e | __float_as_uint(mine.z)) : "memory");
+  }
+  double n[8], m[8], q[8];
+  const long long t0 = clock64();
+  for (uint32_t r = 0; r < a.world; ++r) {
+    const unsigned long long *src = a.xchg[a.rank] + slot + r * src_stride;
+    unsigned long long v0, v1, v2;
+    for (;;) {
+      asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v0) : "l"(src + 0) : "memory");
+      asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v1) : "l"(src + 1) : "memory");
+      asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v2) : "l"(src + 2) : "memory");
+      if ((uint32_t)(v0 >> 32) == a.epoch && (uint32_t)(v1 >> 32) == a.epoch && (uint32_t)(v2 >> 32) == a.epoch) break;
+      if (clock64() - t0 > a.wait_cycles) { atomicOr(a.status, ANODE_ST_WAIT_PEER | ANODE_ST_ABORTED); return; }   // leave a mark, publish nothing
+      __nanosleep(200);
+    }
+    n[r] = DIR == 0 ? (double)(uint32_t)v0 : (double)__uint_as_float((uint32_t)v0);
+    m[r] = (double)__uint_as_float((uint32_t)v1);
+    q[r] = (double)__uint_as_float((uint32_t)v2);
+  }
+  a.mode = MODE_APPLY;
+  a.use_rec = 0;
+  if (DIR == 0) {
+    double sn = 0.0, sm = 0.0, sq = 0.0;
+    for (uint32_t r = 0; r < a.world; ++r) { sn += n[r]; sm += n[r] * m[r]; }
+    const double mean = sm / sn;
+    for (uint32_t r = 0; r < a.world; ++r) { const double d = m[r] - mean; sq += q[r] + n[r] * d * d; }
+    finish_channel_fwd(a, c, sn, mean, sq);
+  } else {
+    double s1 = 0.0, s2 = 0.0;
+    for (uint32_t r = 0; r < a.world; ++r) { s1 += n[r]; s2 += m[r]; }
+    finish_channel_bwd(a, c, s1, s2);
+  }
+}
+
 static size_t gather_bytes(uint32_t C, uint32_t world) { return (size_t)align_up_u64((uint64_t)16 * C * world, 256); }
+
+// True when a kernel with the exchange built in serves this call.
+static bool fused_exchange_applies(const FusedArgs &a, int dir, bool aligned)
+{
+  FusedArgs probe = a;
+  probe.mode = MODE_FUSED;
+  const int kind = pick_kernel_kind(probe, dir, aligned);
+  return kind == ANODE_KERNEL_TILED || kind == ANODE_KERNEL_CLUSTER || kind == ANODE_KERNEL_RESIDENT;
+}
 
 static int run_sync(FusedArgs &a, int dir, bool aligned, AnodeSyncComm *comm, size_t fused_ws_bytes, cudaStream_t stream)
 {
   const NcclApi &api = nccl();
   if (!comm) return ANODE_E_COMM;
-  FusedArgs probe = a;
-  probe.mode = MODE_FUSED;
-  if (comm->world > 1 && comm->xchg_channels >= a.plan.C && (ring_applies(a, dir, aligned) || (tunables().segres && segres_applies(probe, dir, aligned)))) {
-    // One kernel per direction: the block that owns a channel's first tile stores this GPU's
-    // record into every rank's exchange buffer (plain peer stores over NVLink), every block reads
-    // the records of all ranks from its own GPU's buffer.  No collective call, no extra launches.
-    a.mode = MODE_FUSED;
+  const bool exchange = comm->world > 1 && comm->xchg_channels != 0;
+  // Which protocol carries the records is a property of the communicator, never of this rank's shard:
+  // once an exchange buffer is attached every rank uses it (a rank that fell back to NCCL on its own
+  // would enqueue a collective nobody else joins).
+  if (exchange && comm->xchg_channels < a.plan.C) return ANODE_E_COMM;
+  if (exchange) {
     a.rank = (uint32_t)comm->rank; a.world = (uint32_t)comm->world;
     a.xchg_channels = comm->xchg_channels;
-    a.epoch = ++comm->epoch;
+    a.epoch = comm->epoch + 1;
     for (int r = 0; r < comm->world; ++r) a.xchg[r] = comm->xchg[r];
-    return launch_best(a, dir, aligned, stream);
+    int rc;
+    if (fused_exchange_applies(a, dir, aligned)) {
+      // One kernel per direction: the block that owns a channel stores this GPU's record into every
+      // rank's exchange buffer (plain peer stores over NVLink), every block reads the records of all
+      // ranks from its own GPU's buffer.  No collective call, no extra launches.
+      a.mode = MODE_FUSED;
+      rc = launch_best(a, dir, aligned, stream);
+    } else {
+      // reduce kernel, exchange kernel, apply kernel
+      const Plan base = a.plan;
+      const uint32_t world = a.world;
+      a.mode = MODE_STATS; a.world = 1;
+      rc = launch_best(a, dir, aligned, stream);
+      if (rc == ANODE_OK) {
+        const float4 *local = reinterpret_cast<const float4 *>(a.ws + a.plan.off_local);
+        FusedArgs m = a;
+        m.world = world;
+        const uint32_t threads = 128, blocks = (a.plan.C + threads - 1) / threads;
+        if (dir == 0) sync_exchange_kernel<0><<<blocks, threads, 0, stream>>>(m, local);
+        else sync_exchange_kernel<1><<<blocks, threads, 0, stream>>>(m, local);
+        if (cudaGetLastError() != cudaSuccess) rc = ANODE_E_LAUNCH;
+      }
+      if (rc == ANODE_OK) {
+        a.plan = base;
+        a.mode = MODE_APPLY;
+        rc = launch_best(a, dir, aligned, stream);
+      }
+    }
+    // the sequence number advances only when this rank really took part
+    if (rc == ANODE_OK) comm->epoch = a.epoch;
+    return rc;
   }
-  if (!api.ok) return ANODE_E_COMM;
+  if (!api.ok || (comm->world > 1 && !comm->nccl)) return ANODE_E_COMM;
   // the gather buffer sits behind the single-GPU workspace
   float4 *gathered = reinterpret_cast<float4 *>(reinterpret_cast<unsigned char *>(a.status) + fused_ws_bytes);
   const Plan base = a.plan;
@@ -153,6 +244,19 @@ extern "C" int anode_gpu_sync_comm_create(const void *unique_id, int rank, int w
   AnodeSyncComm *c = new AnodeSyncComm{};
   c->rank = rank; c->world = world;
   if (api.CommInitRank(&c->nccl, world, id, rank) != ncclSuccess) { delete c; return ANODE_E_COMM; }
+  *out = c;
+  return ANODE_OK;
+}
+
+// A communicator without NCCL: the records travel through an attached exchange buffer only (callers
+// that set up peer-mapped memory themselves and want no second communication library in the process).
+// Synchronized calls on it fail with ANODE_E_COMM until an exchange buffer is attached.
+extern "C" int anode_gpu_sync_comm_create_exchange_only(int rank, int world, struct AnodeSyncComm **out)
+{
+  if (!out) return ANODE_E_NULL;
+  if (world < 1 || world > 8 || rank < 0 || rank >= world) return ANODE_E_COMM;
+  AnodeSyncComm *c = new AnodeSyncComm{};
+  c->rank = rank; c->world = world;
   *out = c;
   return ANODE_OK;
 }

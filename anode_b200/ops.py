@@ -301,6 +301,20 @@ def relu(x, inplace=False, cfg=None, stream=None):
 # built by the reference (src/ops.rs:105-106).  One kernel per direction.
 # --------------------------------------------------------------------------------------------
 
+KERNELS = {"auto": 0, "tiled": 1, "cluster": 2, "resident": 3, "plain": 4}
+
+
+def set_kernel(name):
+    """Process-wide kernel preference of the fused calls (anode_gpu_batch_norm_fused_set_kernel):
+    'auto', 'tiled', 'cluster', 'resident' or 'plain'.  For tests and measurements."""
+    check(_lib.load().anode_gpu_batch_norm_fused_set_kernel(KERNELS[name]), "anode_gpu_batch_norm_fused_set_kernel")
+
+
+def set_wait_limit_ms(ms):
+    """Bound of the in-kernel waits (anode_gpu_batch_norm_fused_set_wait_limit_ms)."""
+    check(_lib.load().anode_gpu_batch_norm_fused_set_wait_limit_ms(int(ms)), "anode_gpu_batch_norm_fused_set_wait_limit_ms")
+
+
 class Workspace:
     """Caller-owned scratch of the fused kernels (the C ABI allocates nothing)."""
 
@@ -534,9 +548,15 @@ class SyncBatchNormRelu(FusedBatchNormRelu):
 
     @property
     def launches_per_step(self):
-        """Two kernels per step with the in-kernel exchange; otherwise, per direction, reduce kernel,
-        merge kernel and apply kernel (plus one NCCL all-gather)."""
-        return 2 if getattr(self.comm, "_exchange", None) is not None else 6
+        """Two kernels per step where a kernel with the exchange inside serves the shape; otherwise, per
+        direction, reduce kernel, exchange (or merge) kernel and apply kernel."""
+        if getattr(self.comm, "_exchange", None) is None:
+            return 6
+        if self._x is None:
+            return 2
+        d0, c, n = dims_of(self._x)
+        kind = _lib.load().anode_gpu_batch_norm_fused_kernel_kind
+        return sum(1 if kind(d0, c, n, d) != 4 else 3 for d in (0, 1))      # 4: the plain kernel (ANODE_KERNEL_PLAIN)
 
     def step_from_host(self, hx, hdy, hy, hdx, chunk_channels=0):
         """This rank's shard in (page-locked) host memory: whole-shard copies around the two
@@ -561,6 +581,8 @@ class SyncBatchNormRelu(FusedBatchNormRelu):
         super().__init__(channels, **kw)
         if comm is None:
             from .sync import SyncComm
+            from .sync import check_same_on_every_rank
+            check_same_on_every_rank([channels], "channel count of the synchronized layer")
             comm = SyncComm.from_torch_distributed()
             if exchange and comm.world > 1:
                 comm.attach_exchange(channels)       # one kernel per direction, exchange inside it

@@ -50,6 +50,36 @@ def local_moments(x):
     return np.stack([n, mean, m2], axis=1)
 
 
+def check_same_on_every_rank(values, what, group=None):
+    """Host-side guard of the collective contract: every rank must bring the same `values` (e.g. the
+    channel count of a synchronized layer).  All-gathers them over torch.distributed (any backend)
+    and raises AnodeError(ANODE_E_COMM) on every rank when they differ, before anything is enqueued."""
+    import torch
+    import torch.distributed as dist
+    from ._lib import AnodeError
+    world = dist.get_world_size(group)
+    dev = "cuda" if dist.get_backend(group) == "nccl" else "cpu"
+    mine = torch.tensor([int(v) for v in values], dtype=torch.int64, device=dev)
+    allv = [torch.empty_like(mine) for _ in range(world)]
+    dist.all_gather(allv, mine, group=group)
+    if any(not torch.equal(a, allv[0]) for a in allv[1:]):
+        raise AnodeError(-5, "%s differs across ranks: %s" % (what, [a.tolist() for a in allv]))
+
+
+def wait_for_ranks(store, world, rank, key, timeout_s):
+    """Bounded rendezvous on a torch.distributed store before the first synchronized call: every rank
+    announces itself under `key` and waits until all `world` ranks have; a rank that never arrives
+    turns into AnodeError(ANODE_E_COMM) after `timeout_s` seconds instead of a kernel that waits for
+    its records."""
+    import datetime
+    from ._lib import AnodeError
+    store.set("%s/%d" % (key, rank), "1")
+    try:
+        store.wait(["%s/%d" % (key, r) for r in range(world)], datetime.timedelta(seconds=timeout_s))
+    except Exception as e:      # the store raises its own timeout type
+        raise AnodeError(-5, "rendezvous %r: not all %d ranks arrived within %g s (%s)" % (key, world, timeout_s, type(e).__name__))
+
+
 class SyncComm:
     """Communicator of the synchronized entry points (wraps AnodeSyncComm of the C ABI)."""
 
@@ -74,6 +104,24 @@ class SyncComm:
         handle = ctypes.c_void_p()
         check(lib.anode_gpu_sync_comm_create(raw, rank, world, ctypes.byref(handle)), "anode_gpu_sync_comm_create")
         return cls(handle, rank, world)
+
+    @classmethod
+    def exchange_only(cls, rank, world):
+        """A communicator without NCCL (anode_gpu_sync_comm_create_exchange_only): usable once
+        attach_exchange_pointers has been given the world's buffers.  Nothing blocks on the host."""
+        handle = ctypes.c_void_p()
+        check(_lib.load().anode_gpu_sync_comm_create_exchange_only(rank, world, ctypes.byref(handle)),
+              "anode_gpu_sync_comm_create_exchange_only")
+        return cls(handle, rank, world)
+
+    def attach_exchange_pointers(self, buffers, max_channels):
+        """Hands the world's exchange buffers (CUDA uint8 tensors addressable from this process,
+        indexed by rank, each of anode_gpu_sync_exchange_bytes bytes and zeroed once) to the C ABI."""
+        ptrs = (ctypes.c_void_p * self.world)(*[int(b.data_ptr()) for b in buffers])
+        check(_lib.load().anode_gpu_sync_comm_attach_exchange(self.handle, ptrs, max_channels),
+              "anode_gpu_sync_comm_attach_exchange")
+        self._exchange = (buffers, None)
+        return self
 
     def attach_exchange(self, max_channels, group=None):
         """Collective: allocates a peer-visible exchange buffer on every rank (torch symmetric

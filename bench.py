@@ -261,6 +261,88 @@ def time_layer(layer, x, dy, y, dx, steps, warmup, dist, sampler=None):
     return total, fwd, bwd, clocks
 
 
+def parity_check(layer, x, dy, y, dx, dist, device, eps=1e-5):
+    """Numerical check of the last timed step against a float64 computation on the same data, over
+    all ranks: per-channel sums are taken in float64 on every shard and all-reduced (the G-way result
+    must equal the single-device result on the concatenated batch), mean / var / dgamma / dbeta are
+    compared on every channel, y and dx element by element on four channels with the closed form
+    dx = gamma*r*(dz - sum(dz)/M - xhat*sum(dz*xhat)/M).  Tolerance 1e-5 + 1e-4*|want| (channel sums:
+    + 1e-4*rms).  Elements whose pre-activation is within 1e-5 of zero are skipped (mask undecidable
+    in f32).  Also checks that the statistics are bit-identical on every rank."""
+    import torch
+    C = x.shape[1]
+    ax = [0] + list(range(2, x.dim()))
+    bs = [1, -1] + [1] * (x.dim() - 2)
+    step = max(1, min(C, int(64e6 // max(1, x.numel() // C))))
+    s = torch.zeros(2, C, dtype=torch.float64, device=device)
+    for c0 in range(0, C, step):
+        xs = x[:, c0:c0 + step].double()
+        s[0, c0:c0 + step] = xs.sum(dim=ax); s[1, c0:c0 + step] = (xs * xs).sum(dim=ax)
+        del xs
+    cnt = torch.tensor([float(x.numel() // C)], dtype=torch.float64, device=device)
+    if dist is not None:
+        dist.all_reduce(s); dist.all_reduce(cnt)
+    M = float(cnt.item())
+    mean = s[0] / M
+    # second pass about the global mean (float64 sums of squares of N(0,1) data would do, but this is exact for any input)
+    v = torch.zeros(C, dtype=torch.float64, device=device)
+    for c0 in range(0, C, step):
+        d = x[:, c0:c0 + step].double() - mean[c0:c0 + step].view(bs)
+        v[c0:c0 + step] = (d * d).sum(dim=ax)
+        del d
+    if dist is not None:
+        dist.all_reduce(v)
+    var = v / M + eps
+    r = var.rsqrt()
+    g = layer.gamma.double(); b = layer.beta.double()
+    t = torch.zeros(2, C, dtype=torch.float64, device=device)
+    for c0 in range(0, C, step):
+        sl = slice(c0, c0 + step)
+        xh = (x[:, sl].double() - mean[sl].view(bs)) * r[sl].view(bs)
+        dz = dy[:, sl].double() * ((xh * g[sl].view(bs) + b[sl].view(bs)) > 0)
+        t[0, sl] = dz.sum(dim=ax); t[1, sl] = (dz * xh).sum(dim=ax)
+        del xh, dz
+    if dist is not None:
+        dist.all_reduce(t)
+    worst = {"excess": 0.0, "rel": 0.0, "abs": 0.0}
+
+    def cmp(got, want, extra_atol=0.0, skip=None):
+        diff = (got.double() - want).abs()
+        if skip is not None:
+            diff = diff.masked_fill(skip, 0.0)
+        worst["abs"] = max(worst["abs"], float(diff.max()))
+        worst["rel"] = max(worst["rel"], float((diff / (want.abs() + 1e-3)).max()))
+        worst["excess"] = max(worst["excess"], float((diff - 1e-4 * want.abs() - extra_atol).max()))
+
+    cmp(layer.mean, mean); cmp(layer.var, var)
+    cmp(layer.dbeta, t[0], 1e-4 * float(t[0].pow(2).mean().sqrt()))
+    cmp(layer.dgamma, t[1], 1e-4 * float(t[1].pow(2).mean().sqrt()))
+    chans = sorted({0, C // 3, (2 * C) // 3, C - 1})
+    xs = x[:, chans].double(); m4 = mean[chans].view(bs); r4 = r[chans].view(bs); g4 = g[chans].view(bs)
+    xh = (xs - m4) * r4
+    ybn = xh * g4 + b[chans].view(bs)
+    skip = ybn.abs() < 1e-5
+    cmp(y[:, chans], ybn.clamp_min(0.0), skip=skip)
+    dz = dy[:, chans].double() * (ybn > 0)
+    want_dx = g4 * r4 * (dz - t[0][chans].view(bs) / M - xh * t[1][chans].view(bs) / M)
+    cmp(dx[:, chans], want_dx, skip=skip)
+    del xs, xh, ybn, dz, want_dx
+    e = torch.tensor([worst["excess"], worst["rel"], worst["abs"]], dtype=torch.float64, device=device)
+    same = True
+    if dist is not None:
+        dist.all_reduce(e, op=dist.ReduceOp.MAX)
+        world = dist.get_world_size()
+        mine = torch.stack([layer.mean, layer.var, layer.dgamma, layer.dbeta]).contiguous()
+        allv = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(allv, mine)
+        same = all(bool((a.view(torch.int32) == allv[0].view(torch.int32)).all()) for a in allv[1:])
+    excess, rel, ab = [float(q) for q in e.tolist()]
+    return {"ok": bool(excess <= 1e-5 and same), "max_rel": rel, "max_abs": ab, "max_excess_over_1e-4_rel": excess,
+            "stats_bit_identical_across_ranks": same, "channels_checked_elementwise": chans,
+            "against": "float64 torch computation on the concatenated batch (sums all-reduced over ranks)",
+            "tolerance": "1e-5 abs + 1e-4 rel (dgamma/dbeta: + 1e-4 rms)"}
+
+
 def make_layer(ops, channels, world, gamma, beta):
     if world == 1:
         layer = ops.FusedBatchNormRelu(channels, epsilon=1e-5, avg_rate=0.1, affine=True, relu=True)
@@ -271,7 +353,7 @@ def make_layer(ops, channels, world, gamma, beta):
     return layer
 
 
-def bench_workload(ops, name, rank, world, steps, warmup, dist, device, sample_clocks, with_e2e):
+def bench_workload(ops, name, rank, world, steps, warmup, dist, device, sample_clocks, with_e2e, check_parity=True):
     import torch
     w = WORKLOADS[name]
     x, dy, gamma, beta = gen_local(w, rank, world, device)
@@ -286,11 +368,12 @@ def bench_workload(ops, name, rank, world, steps, warmup, dist, device, sample_c
     total, fwd, bwd, status = [float(v) for v in t.tolist()]
     if status != 0:
         raise RuntimeError("device status word %d after the timed region" % int(status))
+    parity = parity_check(layer, x, dy, y, dx, dist, device) if check_parity else None
     n_local = x.numel()
     n_global = n_local * world
     ms = total / steps
     res = {"ms_per_step": ms, "fwd_ms": fwd, "bwd_ms": bwd, "elements_local": n_local, "elements_global": n_global,
-           "value": n_global / (ms * 1e-3), "clocks": clocks, "launches_per_step": layer.launches_per_step}
+           "value": n_global / (ms * 1e-3), "clocks": clocks, "launches_per_step": layer.launches_per_step, "parity": parity}
     if with_e2e:
         res["infer"] = bench_infer(layer, x, y, steps, warmup)
         if world == 1:
@@ -443,8 +526,9 @@ def main():
             d0 *= int(v)
         c, n = int(shp[1]), int(shp[0])
         kind = _lib.load().anode_gpu_batch_norm_fused_kernel_kind(d0, c, n, 0 if direction == "fwd" else 1)
-        return {1: "bn_ring_kernel<%s> (fused reduce+apply, tiled)", 2: "bn_segres_kernel<%s> (fused reduce+apply, clusters)",
-                0: "bn_pipeline_kernel<%s> (fused reduce+apply, plain)"}.get(kind, "?%s") % direction
+        return {3: "bn_resident_kernel<%s> (fused reduce+apply, slices resident in shared memory)",
+                1: "bn_ring_kernel<%s> (fused reduce+apply, tiled)", 2: "bn_segres_kernel<%s> (fused reduce+apply, clusters)",
+                4: "bn_pipeline_kernel<%s> (fused reduce+apply, plain)"}.get(kind, "?%s") % direction
     line = {
         "metric": "bn_relu_fwd_bwd_elements_per_s", "value": main_res["value"], "unit": "elements/s",
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": main_res["ms_per_step"],
@@ -462,6 +546,7 @@ def main():
         "clocks": main_res["clocks"],
         "gpu_launches": main_res["launches_per_step"] * args.steps,
     }
+    line["parity"] = main_res["parity"]
     if "e2e" in main_res:
         line["e2e"] = main_res["e2e"]
     if "infer" in main_res:
@@ -482,7 +567,8 @@ def main():
             torch.cuda.empty_cache()
             r = bench_workload(ops, name, 0, 1, max(5, args.steps // 2), 3, None, device, False, False)
             others[name] = {"value": r["value"], "ms_per_step": r["ms_per_step"], "fwd_ms": r["fwd_ms"], "bwd_ms": r["bwd_ms"],
-                            "step_frac_of_hbm_peak": 20.0 * r["elements_local"] / (r["ms_per_step"] * 1e-3) / 1e9 / peak}
+                            "step_frac_of_hbm_peak": 20.0 * r["elements_local"] / (r["ms_per_step"] * 1e-3) / 1e9 / peak,
+                            "parity_ok": r["parity"]["ok"], "parity_max_rel": r["parity"]["max_rel"]}
         line["other_workloads"] = others
         if rank == 0:
             torch.cuda.empty_cache()
@@ -492,6 +578,10 @@ def main():
     if dist is not None:
         dist.barrier()
         dist.destroy_process_group()
+    bad = [n for n, p in [(args.workload, line["parity"])] + [(n, {"ok": o["parity_ok"]}) for n, o in line.get("other_workloads", {}).items()]
+           if p is not None and not p["ok"]]
+    if bad:
+        raise SystemExit("parity check failed on: %s" % ", ".join(bad))
 
 
 if __name__ == "__main__":

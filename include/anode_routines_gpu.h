@@ -179,14 +179,39 @@ void anode_gpu_positive_clip_flat_map_bwd_f32(
 #define ANODE_ST_WAIT_PEER    2u  /* a wait for another GPU's partials ran out */
 #define ANODE_ST_ABORTED      4u  /* some block saw the bits above and skipped work */
 
+/* Kernels behind the fused calls.  ANODE_KERNEL_AUTO (the default) picks by shape:
+ *   TILED     persistent kernel streaming tiles through a shared-memory ring, re-reading them from L2
+ *             (long 16-byte aligned rows);
+ *   CLUSTER   thread-block clusters keeping a unit's slice in shared memory (short rows, small channels);
+ *   RESIDENT  slices resident in shared memory, all global traffic by bulk copies; takes the residual
+ *             epilogue on long rows, also in synchronized calls;
+ *   PLAIN     plain loads and stores (any shape, any alignment; one GPU).
+ * anode_gpu_batch_norm_fused_set_kernel makes another choice process-wide: that kernel is used wherever
+ * it applies, the automatic choice elsewhere.  Meant for tests and measurements. */
+#define ANODE_KERNEL_AUTO      0
+#define ANODE_KERNEL_TILED     1
+#define ANODE_KERNEL_CLUSTER   2
+#define ANODE_KERNEL_RESIDENT  3
+#define ANODE_KERNEL_PLAIN     4
+int anode_gpu_batch_norm_fused_set_kernel(int kernel);
+
+/* Bound of every wait inside the kernels (for a channel's statistics, for another GPU's records), in
+ * milliseconds of SM clock at 2 GHz; default 1500.  A wait that runs out sets ANODE_ST_WAIT_* and
+ * ANODE_ST_ABORTED in the status word, the kernel drains and returns, and the workspace has to be
+ * re-initialised before its next use.  Process-wide; applies to calls made afterwards. */
+int anode_gpu_batch_norm_fused_set_wait_limit_ms(uint32_t ms);
+
 /* Scratch the fused kernels need for a [dim0, dim1, dim2] problem: per-tile partial
  * statistics, per-channel coefficients, progress counters; one part per direction (each
  * direction keeps state in its part from launch to launch).  A few hundred KB to a few MB. */
 size_t anode_gpu_batch_norm_fused_workspace_bytes(uint32_t dim0, uint32_t dim1, uint32_t dim2);
 
-/* Zeroes a workspace (cudaMemsetAsync on `stream`).  Needed once after allocation and after
- * any call whose status word came back non-zero; the kernels leave the workspace clean
- * otherwise, so back-to-back launches on one stream may share it. */
+/* Zeroes a workspace (cudaMemsetAsync on `stream`).  Needed once after allocation, after any call
+ * whose status word came back non-zero, and whenever the workspace is to serve ANOTHER problem: a
+ * workspace belongs to one (dim0, dim1, dim2) and one alignment class of the tensor pointers (all
+ * 16-byte aligned or not), because the kernels keep state in it from launch to launch that is laid
+ * out by the problem's tile plan.  Otherwise the kernels leave it ready for the next launch, so
+ * back-to-back launches of the same problem on one stream share it. */
 int anode_gpu_batch_norm_fused_workspace_init(void *workspace, size_t bytes, struct CUstream_st *stream);
 
 /* Copies the status word of a workspace to the host (synchronises `stream`). 0 = clean. */
@@ -246,8 +271,8 @@ int anode_gpu_batch_norm_act_fused_bwd_3d1_packed_f32(
  * normalized branch, then positive_clip).  Backward: the mask is taken from the saved output y (as
  * the reference's positive_clip adjoint does, flat_map.cu:187-194); dresidual = dy*mask is the
  * gradient of the shortcut (may be NULL, may alias dy); dx, dgamma, dbeta as in the calls above.
- * Served by the cluster kernel for short rows and by the plain kernel otherwise (12 / 20 algorithmic
- * bytes per element forward / backward). */
+ * Served by the cluster kernel for short rows, by the slice-resident kernel for long 16-byte aligned
+ * rows and by the plain kernel otherwise (12 / 20 algorithmic bytes per element forward / backward). */
 int anode_gpu_batch_norm_add_act_fused_fwd_3d1_packed_f32(
     uint32_t dim0, uint32_t dim1, uint32_t dim2,
     float epsilon, float avg_rate, float neg_slope,
@@ -270,8 +295,9 @@ int anode_gpu_batch_norm_add_act_fused_bwd_3d1_packed_f32(
  * must not call cudaMalloc (it synchronises the device), so neither can provide a workspace.
  * The scratch is a fixed array of ANODE_STATIC_SCRATCH_BYTES inside the library, held on every GPU
  * that loads it until the process exits; this call allocates and frees nothing.
- *   - Problems whose scratch need (anode_gpu_batch_norm_fused_workspace_bytes gives an upper
- *     bound) exceeds the array return ANODE_E_TOO_LARGE and enqueue nothing.
+ *   - Problems whose forward kernel needs more scratch than the array holds return ANODE_E_TOO_LARGE
+ *     and enqueue nothing (half of anode_gpu_batch_norm_fused_workspace_bytes is an upper bound of the
+ *     need; shapes served by the cluster kernel need none).
  *   - All calls on a device share the array, which keeps the previous call's contents; every call
  *     first clears, on `stream`, the part that has to start at zero.  Calls that may overlap on
  *     the GPU (different streams without an ordering between them) race on it: serialise them.
@@ -284,6 +310,10 @@ int anode_gpu_batch_norm_relu_fused_fwd_static_3d1_packed_f32(
     const float *x, const float *gamma, const float *beta,
     float *y, float *mean, float *var, float *run_mean, float *run_var,
     const struct KernelConfig *cfg, struct CUstream_st *stream);
+/* Status word of the built-in array (as anode_gpu_batch_norm_fused_status for a workspace; synchronises
+ * `stream`).  It describes the last call of the entry point above on the current device and is cleared
+ * by the next one, so read it before making another call.  No counterpart in the reference. */
+int anode_gpu_batch_norm_fused_static_status(struct CUstream_st *stream, uint32_t *status);
 
 /* Forward + backward of one layer whose tensors are in HOST memory (no counterpart in the
  * reference, which moves whole arrays with separate copies: MemArray4d -> device array,
@@ -349,6 +379,10 @@ size_t anode_gpu_sync_unique_id_bytes(void);
 int anode_gpu_sync_get_unique_id(void *out);
 int anode_gpu_sync_comm_create(const void *unique_id, int rank, int world, struct AnodeSyncComm **out);
 int anode_gpu_sync_comm_destroy(struct AnodeSyncComm *comm);
+/* The same handle without NCCL behind it, for callers that bring their own peer-mapped memory: the
+ * synchronized calls work once an exchange buffer is attached (below) and return ANODE_E_COMM before;
+ * anode_gpu_sync_allreduce_sum_f32 is not available on it.  Nothing blocks on the host. */
+int anode_gpu_sync_comm_create_exchange_only(int rank, int world, struct AnodeSyncComm **out);
 
 /* In-place sum of buf[0..len) over the ranks (ncclAllReduce on `stream`): the device-side form of
  * SumSpmdOp's host-staged MPI_Allreduce of gradients (src/ops_gpu.rs:538-545,

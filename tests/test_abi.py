@@ -10,9 +10,20 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
 def declared_symbols():
-    src = open(os.path.join(ROOT, "include", "anode_routines_gpu.h")).read()
-    src = re.sub(r"/\*.*?\*/", "", src, flags=re.S)
-    return sorted(set(re.findall(r"\b(anode_gpu_\w+)\s*\(", src)))
+    names = set()
+    for header in ("anode_routines_gpu.h", "anode_routines_gpu_diag.h"):
+        src = open(os.path.join(ROOT, "include", header)).read()
+        src = re.sub(r"/\*.*?\*/", "", src, flags=re.S)
+        names |= set(re.findall(r"\b(anode_gpu_\w+)\s*\(", src))
+    return sorted(names)
+
+
+def test_every_exported_symbol_is_declared_in_a_header():
+    """Nothing is exported behind the headers' back (nm on the built library)."""
+    import subprocess
+    out = subprocess.run(["nm", "-D", "--defined-only", _lib.LIB_PATH], capture_output=True, text=True, check=True).stdout
+    exported = {line.split()[-1] for line in out.splitlines() if " T " in line and line.split()[-1].startswith("anode_")}
+    assert exported == set(declared_symbols()), sorted(exported ^ set(declared_symbols()))
 
 
 def test_header_symbols_are_exported_and_bound():

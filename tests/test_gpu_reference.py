@@ -48,7 +48,9 @@ def _fused(ops, x, dy, rm, rv, gamma=None, beta=None):
     return dict(y=y, dx=dx, mean=mean, var=var, run_mean=rm, run_var=rv)
 
 
-FULL = [  # the benchmark's single-GPU shapes (config 3 and 4 as one GPU of eight sees them)
+FULL = [  # the benchmark's shapes: whole (what one GPU runs alone) and as one GPU of eight sees them
+    ("cfg3", (2048, 256, 56, 56), "normal", 0.0, 1.0),
+    ("cfg5", (1024, 2048, 7, 7), "student3", 0.0, 4.0),
     ("cfg2", (256, 64, 112, 112), "normal", 0.5, 2.0),
     ("cfg3/8", (256, 256, 56, 56), "normal", 0.0, 1.0),
     ("cfg4/8", (4, 32, 16, 128, 128), "normal", 0.0, 1.0),
@@ -78,14 +80,20 @@ def test_fused_matches_reference_kernels_full_size(name, shape, dist, loc, scale
         assert_close(got[k].cpu().numpy(), ref[k].cpu().numpy(), name + " " + k)
     # elementwise on the device: |a-b| <= 1e-5 + 1e-4|b|, skipping elements whose pre-activation
     # is within 1e-5 of zero (mask undecidable in f32)
-    bs = (1, c) + (1,) * (len(shape) - 2)
-    xhat = (x - ref["mean"].view(bs)) * torch.rsqrt(ref["var"].view(bs))
-    skip = xhat.abs() < 1e-5
-    assert float(skip.float().mean()) < 1e-3
-    for k in ("y", "dx"):
-        bad = ((got[k] - ref[k]).abs() > 1e-5 + 1e-4 * ref[k].abs()) & ~skip
-        assert int(bad.sum()) == 0, "%s %s: %d elements off, max diff %g" % (
-            name, k, int(bad.sum()), float((got[k] - ref[k]).abs().max()))
+    step = max(1, int(128e6 // (x.numel() // c)))          # channels per pass: bounds the temporaries
+    nskip = 0
+    for c0 in range(0, c, step):
+        sl = slice(c0, c0 + step)
+        cb = (1, -1) + (1,) * (len(shape) - 2)
+        xhat = (x[:, sl] - ref["mean"][sl].view(cb)) * torch.rsqrt(ref["var"][sl].view(cb))
+        skip = xhat.abs() < 1e-5
+        nskip += int(skip.sum())
+        for k in ("y", "dx"):
+            diff = (got[k][:, sl] - ref[k][:, sl]).abs()
+            bad = (diff > 1e-5 + 1e-4 * ref[k][:, sl].abs()) & ~skip
+            assert int(bad.sum()) == 0, "%s %s: %d elements off, max diff %g" % (name, k, int(bad.sum()), float(diff.max()))
+        del xhat, skip
+    assert nskip < 1e-3 * x.numel()
     # CPU oracle (float64) on four channels
     idx = [0, 1, c // 2, c - 1]
     sub = dict(x=x[:, idx].contiguous().cpu().numpy(), dy=dy[:, idx].contiguous().cpu().numpy())

@@ -31,7 +31,8 @@ def _worker(rank, world, port, shape, axis, out_dir, dist_kind, exchange):
     idx = [slice(None)] * len(shape); idx[axis] = slice(lo, hi)
     x = torch.from_numpy(np.ascontiguousarray(d["x"][tuple(idx)])).cuda()
     dy = torch.from_numpy(np.ascontiguousarray(d["dy"][tuple(idx)])).cuda()
-    layer = ops.SyncBatchNormRelu(shape[1], epsilon=1e-5, avg_rate=0.1, exchange=exchange)
+    per_channel = int(np.prod(shape)) // shape[1]          # shards may be uneven: the global count is stated
+    layer = ops.SyncBatchNormRelu(shape[1], epsilon=1e-5, avg_rate=0.1, exchange=exchange, global_count=per_channel)
     assert layer.launches_per_step == (2 if (exchange and world > 1) else 6)
     layer.gamma.copy_(torch.from_numpy(d["gamma"])); layer.beta.copy_(torch.from_numpy(d["beta"]))
     # twice on one workspace, other data the first time: nothing of a step may reach the next one
@@ -55,10 +56,16 @@ def _worker(rank, world, port, shape, axis, out_dir, dist_kind, exchange):
 
 
 CASES = [((16, 8, 28, 28), 0, "normal"), ((8, 4, 8, 16, 16), 2, "normal"), ((32, 64, 7, 7), 0, "student3"),
-         ((6, 3, 5, 5), 0, "normal")]
+         ((6, 3, 5, 5), 0, "normal"),
+         ((48, 12, 56, 56), 0, "normal"),      # long rows: the slice-resident kernel with the exchange inside
+         ((19, 6, 56, 56), 0, "normal"),       # uneven shards (19 samples over 2, 4 or 8 ranks)
+         ((8, 4, 16, 64, 64), 2, "normal"),    # depth slabs of a volume
+         ((23, 5, 9, 9), 0, "normal")]         # scalar path, uneven shards: reduce kernel, exchange kernel, apply kernel
 
 
 def _run(tmp_path, world, shape, axis, dist_kind, exchange=True):
+    if shape[axis] < world:
+        pytest.skip("fewer items along the sharded axis than ranks")
     port = 30000 + (os.getpid() * 7 + hash((shape, axis, world)) % 997) % 3000
     mp.spawn(_worker, args=(world, port, shape, axis, str(tmp_path), dist_kind, exchange), nprocs=world, join=True)
     d = make_inputs(shape, seed=41, dist=dist_kind, loc=0.5 if dist_kind == "normal" else 0.0,
@@ -84,3 +91,15 @@ def test_sync_world1_matches_oracle(tmp_path, shape, axis, dist_kind):
 @pytest.mark.parametrize("shape,axis,dist_kind", CASES)
 def test_sync_world2_matches_oracle(tmp_path, shape, axis, dist_kind, exchange):
     _run(tmp_path, 2, shape, axis, dist_kind, exchange)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 4, reason="needs four GPUs")
+@pytest.mark.parametrize("shape,axis,dist_kind", CASES)
+def test_sync_world4_matches_oracle(tmp_path, shape, axis, dist_kind):
+    _run(tmp_path, 4, shape, axis, dist_kind, True)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 8, reason="needs eight GPUs")
+@pytest.mark.parametrize("shape,axis,dist_kind", CASES)
+def test_sync_world8_matches_oracle(tmp_path, shape, axis, dist_kind):
+    _run(tmp_path, 8, shape, axis, dist_kind, True)

@@ -122,9 +122,9 @@ def test_cluster_kernel_geometry_invariants():
             ok, cb, cluster, rows, units, smem = list(out)
             kind = lib.anode_gpu_batch_norm_fused_kernel_kind(d0, c, n, direction)
             if not ok:
-                assert kind in (0, 1)
+                assert kind in (1, 4)       # ANODE_KERNEL_TILED, ANODE_KERNEL_PLAIN
                 continue
-            assert kind == 2
+            assert kind == 2                # ANODE_KERNEL_CLUSTER
             assert (cb * d0) % 4 == 0 or cb == c
             assert cb * d0 <= 1024 and 1 <= cb <= max(c, 1)
             assert units == -(-c // cb)
@@ -134,7 +134,7 @@ def test_cluster_kernel_geometry_invariants():
             assert smem >= tensors * rows * min(cb, c) * d0 * 4
     # long aligned rows belong to the tiled kernel, odd strides to the plain one
     assert lib.anode_gpu_batch_norm_fused_kernel_kind(3136, 256, 2048, 0) == 1
-    assert lib.anode_gpu_batch_norm_fused_kernel_kind(117, 5, 3, 1) == 0
+    assert lib.anode_gpu_batch_norm_fused_kernel_kind(117, 5, 3, 1) == 4
     # long aligned rows whose channel fits a few blocks' shared memory: the cluster kernel takes them
     assert lib.anode_gpu_batch_norm_fused_kernel_kind(784, 64, 32, 0) == 2
     assert lib.anode_gpu_batch_norm_fused_kernel_kind(784, 2048, 1024, 0) == 1

@@ -58,3 +58,76 @@ def test_shard_range_partitions_exactly():
             assert max(sizes) - min(sizes) <= 1
     with pytest.raises(ValueError):
         sync.shard_range(8, 2, 2)
+
+
+# ---- failure detection on the host (no GPU): ranks that disagree, a rank that never arrives ----------
+
+def _mismatch_worker(rank, world, port, out_dir):
+    sys.path.insert(0, ROOT)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from anode_b200._lib import AnodeError
+    sync.check_same_on_every_rank([64, 3136], "dims")            # agreeing ranks pass
+    try:
+        sync.check_same_on_every_rank([64 if rank == 0 else 32], "channel count")
+        msg = "no error"
+    except AnodeError as e:
+        msg = "code %d" % e.code
+    with open(os.path.join(out_dir, "r%d.txt" % rank), "w") as f:
+        f.write(msg)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_mismatched_channel_count_is_refused_on_every_rank(tmp_path):
+    port = 29100 + os.getpid() % 1500
+    mp.spawn(_mismatch_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    for r in range(2):
+        assert open(os.path.join(str(tmp_path), "r%d.txt" % r)).read() == "code -5"
+
+
+def _absent_worker(rank, world, port, out_dir):
+    sys.path.insert(0, ROOT)
+    from anode_b200._lib import AnodeError
+    import datetime
+    store = dist.TCPStore("127.0.0.1", port, world, is_master=(rank == 0), timeout=datetime.timedelta(seconds=20))
+    if rank == 1:
+        # this rank dies before the rendezvous: it connects to the store and leaves without announcing itself
+        return
+    import time
+    t0 = time.time()
+    try:
+        sync.wait_for_ranks(store, world, rank, "layer0", timeout_s=1.5)
+        msg = "no error"
+    except AnodeError as e:
+        msg = "code %d after %.1f s" % (e.code, time.time() - t0)
+    with open(os.path.join(out_dir, "r%d.txt" % rank), "w") as f:
+        f.write(msg)
+
+
+def test_rank_that_never_arrives_becomes_an_error_not_a_wait(tmp_path):
+    port = 29300 + os.getpid() % 1500
+    mp.spawn(_absent_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    msg = open(os.path.join(str(tmp_path), "r0.txt")).read()
+    assert msg.startswith("code -5 after"), msg
+    assert float(msg.split()[3]) < 10.0
+
+
+def _present_worker(rank, world, port, out_dir):
+    sys.path.insert(0, ROOT)
+    import datetime
+    store = dist.TCPStore("127.0.0.1", port, world, is_master=(rank == 0), timeout=datetime.timedelta(seconds=20))
+    sync.wait_for_ranks(store, world, rank, "layer0", timeout_s=10.0)
+    with open(os.path.join(out_dir, "r%d.txt" % rank), "w") as f:
+        f.write("ok")
+    if rank == 0:      # keep the store alive until the other rank has read it
+        store.wait(["done/1"], datetime.timedelta(seconds=10))
+    else:
+        store.set("done/1", "1")
+
+
+def test_rendezvous_passes_when_every_rank_arrives(tmp_path):
+    port = 29500 + os.getpid() % 1500
+    mp.spawn(_present_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    assert all(open(os.path.join(str(tmp_path), "r%d.txt" % r)).read() == "ok" for r in range(2))
