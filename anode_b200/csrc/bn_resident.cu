@@ -338,7 +338,7 @@ __device__ __forceinline__ bool pull_merge(const FusedArgs &a, const ResArgs &ra
       uint32_t stop = 0;
       if (lane == 0) {
         if (ctl->abort) stop = 1;
-        else if (clock64() - w0 > a.wait_cycles) { atomicOr(a.status, ANODE_ST_WAIT_STATS); ctl->abort = 1; stop = 1; }
+        else if (clock64() - w0 > 2 * a.wait_cycles) { atomicOr(a.status, ANODE_ST_WAIT_STATS); ctl->abort = 1; stop = 1; }
       }
       if (__shfl_sync(0xffffffffu, stop, 0)) return false;
     }
@@ -456,7 +456,8 @@ __global__ void __launch_bounds__(kResThreads, 1) bn_resident_kernel(const Fused
   const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   uint32_t *status = a.status;
   uint32_t *hdr = reinterpret_cast<uint32_t *>(a.ws);      // [3]: launches of this kernel so far, [4]: exit counter
-  const long long limit = a.wait_cycles;
+  // a wait that depends on another wait gets the longer bound, so that the status word names the root cause
+  const long long limit = 3 * a.wait_cycles;
   const ResBlock rb = res_block(g, blockIdx.x);
   const uint32_t slots0 = s32(sm + kResCtlBytes);
 
@@ -597,6 +598,7 @@ __global__ void __launch_bounds__(kResThreads, 1) bn_resident_kernel(const Fused
       }
       // consumers look at a slot's barrier only once its load has been issued (see wait_load)
       __syncwarp();
+      ++nload;
       if (lane == 0) { __threadfence_block(); ctl->issued = nload; }
       return true;
     });
