@@ -81,11 +81,16 @@ SIGNATURES = {
         (c_int, _D + [f32, f32, c_int] + [vp] * 8 + [vp, vp, size_t] + _T),
     "anode_gpu_sync_batch_norm_relu_bwd_3d1_packed_f32":
         (c_int, _D + [ctypes.c_uint64, c_int, c_int] + [vp] * 9 + [vp, vp, size_t] + _T),
+    "anode_gpu_sync_batch_norm_add_act_fwd_3d1_packed_f32":
+        (c_int, _D + [f32, f32, f32] + [vp] * 9 + [vp, vp, size_t] + _T),
+    "anode_gpu_sync_batch_norm_add_act_bwd_3d1_packed_f32":
+        (c_int, _D + [ctypes.c_uint64, f32, c_int] + [vp] * 11 + [vp, vp, size_t] + _T),
     "anode_gpu_batch_norm_fused_plan": (c_int, _D + [c_int, u32, u32, u32, ctypes.POINTER(u32), u32]),
     "anode_gpu_batch_norm_fused_plan_walk":
         (c_int, _D + [c_int, u32, u32, u32, u32, u32, ctypes.POINTER(ctypes.c_uint64)]),
     "anode_gpu_batch_norm_segres_geometry": (c_int, _D + [c_int, ctypes.POINTER(u32)]),
     "anode_gpu_batch_norm_fused_kernel_kind": (c_int, _D + [c_int]),
+    "anode_gpu_batch_norm_add_act_fused_kernel_kind": (c_int, _D + [c_int]),
     "anode_gpu_batch_norm_fused_set_wait_limit_ms": (c_int, [u32]),
     "anode_gpu_batch_norm_fused_set_kernel": (c_int, [c_int]),
     "anode_gpu_batch_norm_resident_plan": (c_int, _D + [u32, ctypes.POINTER(u32)]),

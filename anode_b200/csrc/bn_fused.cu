@@ -225,10 +225,11 @@ int pick_kernel_kind(const FusedArgs &a, int dir, bool aligned)
     default: break;
   }
   if (extra) {
-    // short rows: the cluster kernel; long rows: the slice-resident kernel; the rest: the plain kernel
+    // short rows: the cluster kernel; otherwise the plain kernel on one GPU (measured faster there) and
+    // the slice-resident kernel, which has the exchange inside, in synchronized calls
     if (segres_applies(a, dir, aligned)) return ANODE_KERNEL_CLUSTER;
-    if (resident_applies(a, dir, aligned)) return ANODE_KERNEL_RESIDENT;
-    return plain_ok ? ANODE_KERNEL_PLAIN : -1;
+    if (plain_ok) return ANODE_KERNEL_PLAIN;
+    return resident_applies(a, dir, aligned) ? ANODE_KERNEL_RESIDENT : -1;
   }
   // short rows, and channels small enough to sit in a few blocks' shared memory: the cluster kernel
   if (segres_preferred(a, dir, aligned)) return ANODE_KERNEL_CLUSTER;
@@ -532,6 +533,19 @@ extern "C" int anode_gpu_batch_norm_fused_kernel_kind(uint32_t dim0, uint32_t di
   a.plan = plan_for(dim0, dim1, dim2, true);
   a.mode = MODE_FUSED;
   a.ws_capacity = workspace_part_bytes(dim0, dim1, dim2);
+  return pick_kernel_kind(a, dir, true);
+}
+
+// The same for the residual-epilogue calls (anode_gpu_batch_norm_add_act_fused_*).
+extern "C" int anode_gpu_batch_norm_add_act_fused_kernel_kind(uint32_t dim0, uint32_t dim1, uint32_t dim2, int dir)
+{
+  if (check_dims(dim0, dim1, dim2)) return ANODE_E_DIMS;
+  static const float dummy = 0.f;
+  FusedArgs a{};
+  a.plan = plan_for(dim0, dim1, dim2, true);
+  a.mode = MODE_FUSED;
+  a.ws_capacity = workspace_part_bytes(dim0, dim1, dim2);
+  if (dir == 0) a.res = &dummy; else a.ymask = &dummy;       // only their presence matters here
   return pick_kernel_kind(a, dir, true);
 }
 

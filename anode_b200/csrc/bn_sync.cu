@@ -348,3 +348,56 @@ extern "C" int anode_gpu_sync_batch_norm_relu_bwd_3d1_packed_f32(
   a.count_total = (double)global_count;
   return run_sync(a, 1, aligned16(x) && aligned16(dy) && aligned16(dx), comm, fused, stream);
 }
+
+// Residual-block epilogue across GPUs: anode_gpu_batch_norm_add_act_fused_{fwd,bwd}_3d1_packed_f32 with the
+// statistics and the backward sums taken over all ranks' shards.
+extern "C" int anode_gpu_sync_batch_norm_add_act_fwd_3d1_packed_f32(
+    uint32_t dim0, uint32_t dim1, uint32_t dim2, float epsilon, float avg_rate, float neg_slope,
+    const float *x, const float *residual, const float *gamma, const float *beta,
+    float *y, float *mean, float *var, float *run_mean, float *run_var,
+    struct AnodeSyncComm *comm, void *workspace, size_t workspace_bytes,
+    const struct KernelConfig *cfg, struct CUstream_st *stream)
+{
+  (void)cfg;
+  if (!comm) return ANODE_E_COMM;
+  if (!residual) return ANODE_E_NULL;
+  if (!aligned4(residual)) return ANODE_E_ALIGN;
+  const size_t fused = anode_gpu_batch_norm_fused_workspace_bytes(dim0, dim1, dim2);
+  if (fused == 0) return ANODE_E_DIMS;
+  if (workspace_bytes < fused + gather_bytes(dim1, (uint32_t)comm->world)) return ANODE_E_WORKSPACE;
+  FusedArgs a;
+  const int rc = prepare_fwd(a, dim0, dim1, dim2, epsilon, avg_rate, 1, x, gamma, beta, y, mean, var,
+                             run_mean, run_var, workspace, fused);
+  if (rc) return rc;
+  a.neg_slope = neg_slope;
+  a.res = residual;
+  const bool al = aligned16(x) && aligned16(y) && aligned16(residual);
+  if (!al) a.plan = plan_for(dim0, dim1, dim2, false);
+  return run_sync(a, 0, al, comm, fused, stream);
+}
+
+extern "C" int anode_gpu_sync_batch_norm_add_act_bwd_3d1_packed_f32(
+    uint32_t dim0, uint32_t dim1, uint32_t dim2, uint64_t global_count, float neg_slope, int accumulate,
+    const float *dy, const float *x, const float *y, const float *mean, const float *var,
+    const float *gamma, const float *beta, float *dx, float *dresidual, float *dgamma, float *dbeta,
+    struct AnodeSyncComm *comm, void *workspace, size_t workspace_bytes,
+    const struct KernelConfig *cfg, struct CUstream_st *stream)
+{
+  (void)cfg;
+  if (!comm) return ANODE_E_COMM;
+  if (!y) return ANODE_E_NULL;
+  if (!aligned4(y) || (dresidual && !aligned4(dresidual))) return ANODE_E_ALIGN;
+  const size_t fused = anode_gpu_batch_norm_fused_workspace_bytes(dim0, dim1, dim2);
+  if (fused == 0 || global_count < (uint64_t)dim0 * dim2) return ANODE_E_DIMS;
+  if (workspace_bytes < fused + gather_bytes(dim1, (uint32_t)comm->world)) return ANODE_E_WORKSPACE;
+  FusedArgs a;
+  const int rc = prepare_bwd(a, dim0, dim1, dim2, 1, accumulate, dy, x, mean, var, gamma, beta, dx,
+                             dgamma, dbeta, workspace, fused);
+  if (rc) return rc;
+  a.neg_slope = neg_slope;
+  a.ymask = y; a.dres = dresidual;
+  a.count_total = (double)global_count;
+  const bool al = aligned16(x) && aligned16(dy) && aligned16(dx) && aligned16(y) && (!dresidual || aligned16(dresidual));
+  if (!al) a.plan = plan_for(dim0, dim1, dim2, false);
+  return run_sync(a, 1, al, comm, fused, stream);
+}

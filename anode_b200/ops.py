@@ -607,6 +607,33 @@ class SyncBatchNormRelu(FusedBatchNormRelu):
         self._x = x
         return y
 
+    def forward_add(self, x, residual, out=None, neg_slope=0.0):
+        """y = act(bn(x) + residual) with statistics over all ranks (the residual-block epilogue)."""
+        d0, c, n = dims_of(x)
+        y = out if out is not None else torch.empty_like(x)
+        ws = self._workspace(x)
+        check(_lib.load().anode_gpu_sync_batch_norm_add_act_fwd_3d1_packed_f32(
+            d0, c, n, ctypes.c_float(self.epsilon), ctypes.c_float(self.avg_rate), ctypes.c_float(neg_slope),
+            _p(x), _p(residual), _p(self.gamma), _p(self.beta), _p(y), _p(self.mean), _p(self.var), _p(self.avg_mean),
+            _p(self.avg_var), self.comm.handle, ws.ptr, ws.bytes, _cfg(None), _stream(None)),
+            "anode_gpu_sync_batch_norm_add_act_fwd_3d1_packed_f32")
+        self._x, self._y = x, y
+        return y
+
+    def backward_add(self, dy, out=None, dresidual=None, neg_slope=0.0):
+        """Adjoint of forward_add: returns (dx, dresidual); the mask comes from the saved output."""
+        x, y = self._x, self._y
+        d0, c, n = dims_of(x)
+        dx = out if out is not None else torch.empty_like(x)
+        ws = self._workspace(x)
+        total = self.global_count if self.global_count is not None else d0 * n * self.comm.world
+        check(_lib.load().anode_gpu_sync_batch_norm_add_act_bwd_3d1_packed_f32(
+            d0, c, n, ctypes.c_uint64(total), ctypes.c_float(neg_slope), 0,
+            _p(dy), _p(x), _p(y), _p(self.mean), _p(self.var), _p(self.gamma), _p(self.beta), _p(dx), _p(dresidual),
+            _p(self.dgamma), _p(self.dbeta), self.comm.handle, ws.ptr, ws.bytes, _cfg(None), _stream(None)),
+            "anode_gpu_sync_batch_norm_add_act_bwd_3d1_packed_f32")
+        return dx, dresidual
+
     def backward(self, dy, out=None):
         x = self._x
         d0, c, n = dims_of(x)

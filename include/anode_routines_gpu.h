@@ -427,6 +427,27 @@ int anode_gpu_sync_batch_norm_relu_bwd_3d1_packed_f32(
     struct AnodeSyncComm *comm, void *workspace, size_t workspace_bytes,
     const struct KernelConfig *cfg, struct CUstream_st *stream);
 
+/* The residual-block epilogue of anode_gpu_batch_norm_add_act_fused_{fwd,bwd}_3d1_packed_f32 with
+ * statistics and backward sums over all ranks: y = act(bn(x) + residual) per shard (shortcut plus
+ * normalized branch, then positive_clip: examples/run_imagenet_mpi.rs:191-195, 224-226, which the
+ * reference trains data-parallel).  On long 16-byte aligned rows one kernel per direction (the
+ * slice-resident kernel with the exchange inside), on short rows the cluster kernel, otherwise reduce
+ * kernel, exchange kernel, apply kernel. */
+int anode_gpu_sync_batch_norm_add_act_fwd_3d1_packed_f32(
+    uint32_t dim0, uint32_t dim1, uint32_t dim2,
+    float epsilon, float avg_rate, float neg_slope,
+    const float *x, const float *residual, const float *gamma, const float *beta,
+    float *y, float *mean, float *var, float *run_mean, float *run_var,
+    struct AnodeSyncComm *comm, void *workspace, size_t workspace_bytes,
+    const struct KernelConfig *cfg, struct CUstream_st *stream);
+int anode_gpu_sync_batch_norm_add_act_bwd_3d1_packed_f32(
+    uint32_t dim0, uint32_t dim1, uint32_t dim2, uint64_t global_count, float neg_slope, int accumulate,
+    const float *dy, const float *x, const float *y, const float *mean, const float *var,
+    const float *gamma, const float *beta,
+    float *dx, float *dresidual, float *dgamma, float *dbeta,
+    struct AnodeSyncComm *comm, void *workspace, size_t workspace_bytes,
+    const struct KernelConfig *cfg, struct CUstream_st *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -16,6 +16,9 @@ extern "C" {
  * aligned tensors on one GPU: an ANODE_KERNEL_* value of anode_routines_gpu.h. */
 int anode_gpu_batch_norm_fused_kernel_kind(uint32_t dim0, uint32_t dim1, uint32_t dim2, int dir);
 
+/* The same for the residual-epilogue calls (anode_gpu_batch_norm_add_act_fused_*). */
+int anode_gpu_batch_norm_add_act_fused_kernel_kind(uint32_t dim0, uint32_t dim1, uint32_t dim2, int dir);
+
 /* Tile plan of the tiled and plain kernels.  out (15 values): regime, vec, cb, units, rows_per_tile,
  * piece_len, pieces, sample_blocks, tiles_per_unit, total_tiles, grid, lookahead_steps, div_mul,
  * workspace bytes (low, high).  Zero for resident_blocks / tile_floats / slack_steps = the library's

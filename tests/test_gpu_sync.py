@@ -103,3 +103,69 @@ def test_sync_world4_matches_oracle(tmp_path, shape, axis, dist_kind):
 @pytest.mark.parametrize("shape,axis,dist_kind", CASES)
 def test_sync_world8_matches_oracle(tmp_path, shape, axis, dist_kind):
     _run(tmp_path, 8, shape, axis, dist_kind, True)
+
+
+# ---- the residual-block epilogue across GPUs -----------------------------------------------------------
+
+def _residual_worker(rank, world, port, shape, axis, out_dir):
+    sys.path.insert(0, ROOT)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    from anode_b200 import ops, sync
+    d = make_inputs(shape, seed=43, loc=0.3, scale=1.5)
+    res_h = np.random.default_rng(44).standard_normal(shape).astype(np.float32)
+    lo, hi = sync.shard_range(shape[axis], rank, world)
+    idx = [slice(None)] * len(shape); idx[axis] = slice(lo, hi)
+    cut = lambda a: torch.from_numpy(np.ascontiguousarray(a[tuple(idx)])).cuda()
+    x, dy, res = cut(d["x"]), cut(d["dy"]), cut(res_h)
+    layer = ops.SyncBatchNormRelu(shape[1], epsilon=1e-5, avg_rate=0.1, global_count=int(np.prod(shape)) // shape[1])
+    layer.gamma.copy_(torch.from_numpy(d["gamma"])); layer.beta.copy_(torch.from_numpy(d["beta"]))
+    for _ in range(2):      # twice on one workspace
+        layer.avg_mean.zero_(); layer.avg_var.fill_(1.0)
+        y = layer.forward_add(x, res)
+        dx, dres = layer.backward_add(dy, dresidual=torch.empty_like(x))
+    torch.cuda.synchronize()
+    assert layer.status() == 0
+    np.savez(os.path.join(out_dir, "r%d.npz" % rank), y=y.cpu().numpy(), dx=dx.cpu().numpy(), dres=dres.cpu().numpy(),
+             mean=layer.mean.cpu().numpy(), var=layer.var.cpu().numpy(), run_mean=layer.avg_mean.cpu().numpy(),
+             run_var=layer.avg_var.cpu().numpy(), dgamma=layer.dgamma.cpu().numpy(), dbeta=layer.dbeta.cpu().numpy())
+    dist.barrier()
+    layer.comm.destroy()
+    dist.destroy_process_group()
+
+
+RESIDUAL_CASES = [((24, 6, 56, 56), 0),      # long rows: the slice-resident kernel, exchange inside
+                  ((32, 64, 7, 7), 0),       # short rows: the cluster kernel, exchange inside
+                  ((10, 3, 5, 5), 0)]        # scalar path: reduce kernel, exchange kernel, apply kernel
+
+
+@pytest.mark.parametrize("world", [1, 2, 4, 8])
+@pytest.mark.parametrize("shape,axis", RESIDUAL_CASES)
+def test_sync_residual_epilogue_matches_oracle(tmp_path, shape, axis, world):
+    from tests.util import assert_close, assert_sum_close
+    if torch.cuda.device_count() < world:
+        pytest.skip("needs %d GPUs" % world)
+    port = 33000 + (os.getpid() * 5 + hash((shape, world)) % 997) % 3000
+    mp.spawn(_residual_worker, args=(world, port, shape, axis, str(tmp_path)), nprocs=world, join=True)
+    d = make_inputs(shape, seed=43, loc=0.3, scale=1.5)
+    res_h = np.random.default_rng(44).standard_normal(shape).astype(np.float32)
+    truth = o.bn_add_act_fwd_bwd_f64(d["x"], res_h, d["dy"], 1e-5, 0.1, d["run_mean"], d["run_var"], d["gamma"], d["beta"], neg_slope=0.0)
+    parts = [np.load(os.path.join(str(tmp_path), "r%d.npz" % r)) for r in range(world)]
+    c = shape[1]
+    bs = (1, c) + (1,) * (len(shape) - 2)
+    pre = ((d["x"].astype(np.float64) - truth["mean"].reshape(bs)) / np.sqrt(truth["var"]).reshape(bs)
+           * d["gamma"].astype(np.float64).reshape(bs) + d["beta"].astype(np.float64).reshape(bs) + res_h)
+    skip = np.abs(pre) < 1e-5
+    for k in ("mean", "var", "run_mean", "run_var"):
+        for p in parts:
+            assert (p[k] == parts[0][k]).all(), k
+        assert_close(parts[0][k], truth[k], k)
+    cat = lambda k: np.concatenate([p[k] for p in parts], axis=axis)
+    assert_close(cat("y"), truth["y"], "y", skip=skip)
+    assert_close(cat("dx"), truth["dx"], "dx", skip=skip)
+    assert_close(cat("dres"), truth["dresidual"], "dresidual", skip=skip)
+    assert_sum_close(parts[0]["dgamma"], truth["dgamma"], "dgamma")
+    assert_sum_close(parts[0]["dbeta"], truth["dbeta"], "dbeta")
