@@ -85,6 +85,10 @@ SIGNATURES = {
         (c_int, _D + [f32, f32, f32] + [vp] * 9 + [vp, vp, size_t] + _T),
     "anode_gpu_sync_batch_norm_add_act_bwd_3d1_packed_f32":
         (c_int, _D + [ctypes.c_uint64, f32, c_int] + [vp] * 11 + [vp, vp, size_t] + _T),
+    "anode_gpu_sync_batch_norm_host_step_staging_bytes": (size_t, _D + [ctypes.c_uint64, vp, u32]),
+    "anode_gpu_sync_batch_norm_host_step_blocks": (u32, _D + [ctypes.c_uint64, vp, u32]),
+    "anode_gpu_sync_batch_norm_relu_step_host_3d1_packed_f32":
+        (c_int, _D + [ctypes.c_uint64, f32, f32, c_int] + [vp] * 12 + [vp, vp, size_t, u32] + _T),
     "anode_gpu_batch_norm_fused_plan": (c_int, _D + [c_int, u32, u32, u32, ctypes.POINTER(u32), u32]),
     "anode_gpu_batch_norm_fused_plan_walk":
         (c_int, _D + [c_int, u32, u32, u32, u32, u32, ctypes.POINTER(ctypes.c_uint64)]),

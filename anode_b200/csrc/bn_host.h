@@ -58,4 +58,9 @@ int launch_resident(FusedArgs &a, int dir, uint64_t ws_off, cudaStream_t stream)
 long long wait_limit_cycles();
 uint64_t control_region_bytes(uint32_t dim0, uint32_t C, uint32_t N, bool aligned);
 
+// synchronized launches (bn_sync.cu), for the host-buffer step
+int sync_launch(FusedArgs &a, int dir, bool aligned, struct ::AnodeSyncComm *comm, size_t fused_ws_bytes, cudaStream_t stream);
+size_t sync_gather_bytes(uint32_t C, const struct ::AnodeSyncComm *comm);
+int sync_world(const struct ::AnodeSyncComm *comm);
+
 }  // namespace anode_b200

@@ -67,14 +67,18 @@ struct StageLayout {
   uint64_t total;
 };
 
-static bool stage_layout(uint32_t dim0, uint32_t C, uint32_t N, uint32_t chunk, StageLayout &L)
+// `samples_for_chunk`: the sample count the default block size is derived from (with several GPUs the
+// same number on every rank, so that all ranks cut the layer into the same blocks); `gather`: bytes
+// behind the workspace that a synchronized launch may need for its records.
+static bool stage_layout(uint32_t dim0, uint32_t C, uint32_t N, uint32_t chunk, StageLayout &L,
+                         uint32_t samples_for_chunk = 0, const AnodeSyncComm *comm = nullptr)
 {
-  if (chunk == 0) chunk = default_chunk(dim0, C, N);
+  if (chunk == 0) chunk = default_chunk(dim0, C, samples_for_chunk ? samples_for_chunk : N);
   if (chunk > C) chunk = C;
   L.chunk = chunk;
   const uint32_t tail = C % chunk;
-  uint64_t ws = 2 * workspace_part_bytes(dim0, chunk, N);
-  if (tail) { const uint64_t w = 2 * workspace_part_bytes(dim0, tail, N); if (w > ws) ws = w; }
+  uint64_t ws = 2 * workspace_part_bytes(dim0, chunk, N) + sync_gather_bytes(chunk, comm);
+  if (tail) { const uint64_t w = 2 * workspace_part_bytes(dim0, tail, N) + sync_gather_bytes(tail, comm); if (w > ws) ws = w; }
   L.ws_bytes = align_up_u64(ws, 256);
   L.tensor_bytes = align_up_u64((uint64_t)dim0 * chunk * N * 4, 256);
   L.total = L.ws_bytes + (uint64_t)kStageBufs * 3 * L.tensor_bytes;      // per buffer: x, dy (dx in place), y
@@ -122,22 +126,29 @@ extern "C" uint32_t anode_gpu_batch_norm_host_step_blocks(uint32_t dim0, uint32_
   return ceil_div_u32(dim1, L.chunk);
 }
 
-extern "C" int anode_gpu_batch_norm_relu_fused_step_host_3d1_packed_f32(
-    uint32_t dim0, uint32_t dim1, uint32_t dim2, float epsilon, float avg_rate, int relu,
-    const float *host_x, const float *host_dy, const float *gamma, const float *beta,
-    float *host_y, float *host_dx,
-    float *mean, float *var, float *run_mean, float *run_var, float *dgamma, float *dbeta,
-    void *staging, size_t staging_bytes, uint32_t chunk_channels,
-    const struct KernelConfig *cfg, struct CUstream_st *stream)
+// Number of samples per rank the block size of a synchronized step is derived from.
+static uint32_t sync_chunk_samples(uint32_t dim0, uint64_t global_count, const AnodeSyncComm *comm)
 {
-  (void)cfg;
+  const uint64_t per_rank = global_count / ((uint64_t)dim0 * (uint64_t)sync_world(comm));
+  return per_rank ? (uint32_t)per_rank : 1u;
+}
+
+// The step, on one GPU (comm == nullptr) or synchronized over the ranks of `comm`: every rank then makes
+// the same sequence of synchronized launches, one pair per channel block.
+static int host_step(uint32_t dim0, uint32_t dim1, uint32_t dim2, uint64_t global_count, float epsilon, float avg_rate, int relu,
+                     const float *host_x, const float *host_dy, const float *gamma, const float *beta,
+                     float *host_y, float *host_dx,
+                     float *mean, float *var, float *run_mean, float *run_var, float *dgamma, float *dbeta,
+                     AnodeSyncComm *comm, void *staging, size_t staging_bytes, uint32_t chunk_channels, cudaStream_t stream)
+{
   const int drc = check_dims(dim0, dim1, dim2);
   if (drc) return drc;
   if (!host_x || !host_dy || !host_y || !host_dx || !mean || !var) return ANODE_E_NULL;
   if (!aligned4(host_x) || !aligned4(host_dy) || !aligned4(host_y) || !aligned4(host_dx)) return ANODE_E_ALIGN;
   if (!staging || (reinterpret_cast<uintptr_t>(staging) & 255u)) return ANODE_E_WORKSPACE;
+  if (comm && global_count < (uint64_t)dim0 * dim2) return ANODE_E_DIMS;
   StageLayout L;
-  stage_layout(dim0, dim1, dim2, chunk_channels, L);
+  stage_layout(dim0, dim1, dim2, chunk_channels, L, comm ? sync_chunk_samples(dim0, global_count, comm) : 0, comm);
   if (staging_bytes < L.total) return ANODE_E_WORKSPACE;
 
   std::lock_guard<std::mutex> lock(g_pipe_mu);
@@ -172,17 +183,19 @@ extern "C" int anode_gpu_batch_norm_relu_fused_step_host_3d1_packed_f32(
       ANODE_TRY(cudaMemsetAsync(ws + 256, 0, L.ws_bytes - 256, stream));
     prev_cc = cc;
     FusedArgs a;
+    const size_t fused = (size_t)(2 * workspace_part_bytes(dim0, cc, dim2));      // the records of a synchronized launch sit behind it
     int rc = prepare_fwd(a, dim0, cc, dim2, epsilon, avg_rate, relu, tensor(b, 0), gamma ? gamma + c0 : nullptr,
                          (gamma && beta) ? beta + c0 : nullptr, tensor(b, 2), mean + c0, var + c0,
-                         run_mean ? run_mean + c0 : nullptr, run_var ? run_var + c0 : nullptr, ws, L.ws_bytes);
+                         run_mean ? run_mean + c0 : nullptr, run_var ? run_var + c0 : nullptr, ws, fused);
     if (rc) return rc;
-    rc = launch_best(a, 0, true, stream);
+    rc = comm ? sync_launch(a, 0, true, comm, fused, stream) : launch_best(a, 0, true, stream);
     if (rc) return rc;
     rc = prepare_bwd(a, dim0, cc, dim2, relu, 0, dx_, tensor(b, 0), mean + c0, var + c0, gamma ? gamma + c0 : nullptr,
                      (gamma && beta) ? beta + c0 : nullptr, dx_, dgamma ? dgamma + c0 : nullptr,
-                     dbeta ? dbeta + c0 : nullptr, ws, L.ws_bytes);
+                     dbeta ? dbeta + c0 : nullptr, ws, fused);
     if (rc) return rc;
-    rc = launch_best(a, 1, true, stream);
+    if (comm) a.count_total = (double)global_count;
+    rc = comm ? sync_launch(a, 1, true, comm, fused, stream) : launch_best(a, 1, true, stream);
     if (rc) return rc;
     ANODE_TRY(cudaEventRecord(P->k_done[b], stream));
     // device -> host
@@ -195,4 +208,52 @@ extern "C" int anode_gpu_batch_norm_relu_fused_step_host_3d1_packed_f32(
   for (int b = 0; b < kStageBufs && (uint32_t)b < nchunks; ++b) ANODE_TRY(cudaStreamWaitEvent(stream, P->out_done[b], 0));
 #undef ANODE_TRY
   return ANODE_OK;
+}
+
+extern "C" int anode_gpu_batch_norm_relu_fused_step_host_3d1_packed_f32(
+    uint32_t dim0, uint32_t dim1, uint32_t dim2, float epsilon, float avg_rate, int relu,
+    const float *host_x, const float *host_dy, const float *gamma, const float *beta,
+    float *host_y, float *host_dx,
+    float *mean, float *var, float *run_mean, float *run_var, float *dgamma, float *dbeta,
+    void *staging, size_t staging_bytes, uint32_t chunk_channels,
+    const struct KernelConfig *cfg, struct CUstream_st *stream)
+{
+  (void)cfg;
+  return host_step(dim0, dim1, dim2, 0, epsilon, avg_rate, relu, host_x, host_dy, gamma, beta, host_y, host_dx, mean, var,
+                   run_mean, run_var, dgamma, dbeta, nullptr, staging, staging_bytes, chunk_channels, stream);
+}
+
+// The same step for one rank's shard of a batch sharded over the ranks of `comm`: the kernels of every
+// channel block are the synchronized ones, so statistics and backward sums are those of the global
+// batch while each rank's copies overlap with its kernels as above.
+extern "C" size_t anode_gpu_sync_batch_norm_host_step_staging_bytes(uint32_t dim0, uint32_t dim1, uint32_t dim2, uint64_t global_count,
+                                                                    struct AnodeSyncComm *comm, uint32_t chunk_channels)
+{
+  if (!comm || check_dims(dim0, dim1, dim2) || global_count < (uint64_t)dim0 * dim2) return 0;
+  StageLayout L;
+  stage_layout(dim0, dim1, dim2, chunk_channels, L, sync_chunk_samples(dim0, global_count, comm), comm);
+  return (size_t)L.total;
+}
+
+extern "C" uint32_t anode_gpu_sync_batch_norm_host_step_blocks(uint32_t dim0, uint32_t dim1, uint32_t dim2, uint64_t global_count,
+                                                               struct AnodeSyncComm *comm, uint32_t chunk_channels)
+{
+  if (!comm || check_dims(dim0, dim1, dim2) || global_count < (uint64_t)dim0 * dim2) return 0;
+  StageLayout L;
+  stage_layout(dim0, dim1, dim2, chunk_channels, L, sync_chunk_samples(dim0, global_count, comm), comm);
+  return ceil_div_u32(dim1, L.chunk);
+}
+
+extern "C" int anode_gpu_sync_batch_norm_relu_step_host_3d1_packed_f32(
+    uint32_t dim0, uint32_t dim1, uint32_t dim2, uint64_t global_count, float epsilon, float avg_rate, int relu,
+    const float *host_x, const float *host_dy, const float *gamma, const float *beta,
+    float *host_y, float *host_dx,
+    float *mean, float *var, float *run_mean, float *run_var, float *dgamma, float *dbeta,
+    struct AnodeSyncComm *comm, void *staging, size_t staging_bytes, uint32_t chunk_channels,
+    const struct KernelConfig *cfg, struct CUstream_st *stream)
+{
+  (void)cfg;
+  if (!comm) return ANODE_E_COMM;
+  return host_step(dim0, dim1, dim2, global_count, epsilon, avg_rate, relu, host_x, host_dy, gamma, beta, host_y, host_dx, mean, var,
+                   run_mean, run_var, dgamma, dbeta, comm, staging, staging_bytes, chunk_channels, stream);
 }

@@ -156,7 +156,12 @@ static int run_sync(FusedArgs &a, int dir, bool aligned, AnodeSyncComm *comm, si
 {
   const NcclApi &api = nccl();
   if (!comm) return ANODE_E_COMM;
-  const bool exchange = comm->world > 1 && comm->xchg_channels != 0;
+  if (comm->world == 1) {
+    // nothing to exchange: the one-GPU launch
+    a.mode = MODE_FUSED;
+    return launch_best(a, dir, aligned, stream);
+  }
+  const bool exchange = comm->xchg_channels != 0;
   // Which protocol carries the records is a property of the communicator, never of this rank's shard:
   // once an exchange buffer is attached every rank uses it (a rank that fell back to NCCL on its own
   // would enqueue a collective nobody else joins).
@@ -198,7 +203,7 @@ static int run_sync(FusedArgs &a, int dir, bool aligned, AnodeSyncComm *comm, si
     if (rc == ANODE_OK) comm->epoch = a.epoch;
     return rc;
   }
-  if (!api.ok || (comm->world > 1 && !comm->nccl)) return ANODE_E_COMM;
+  if (!api.ok || !comm->nccl) return ANODE_E_COMM;
   // the gather buffer sits behind the single-GPU workspace
   float4 *gathered = reinterpret_cast<float4 *>(reinterpret_cast<unsigned char *>(a.status) + fused_ws_bytes);
   const Plan base = a.plan;
@@ -216,6 +221,14 @@ static int run_sync(FusedArgs &a, int dir, bool aligned, AnodeSyncComm *comm, si
   a.mode = MODE_APPLY;
   return launch_best(a, dir, aligned, stream);
 }
+
+// What the host-buffer step (bn_hoststep.cu) needs of this file.
+int sync_launch(FusedArgs &a, int dir, bool aligned, AnodeSyncComm *comm, size_t fused_ws_bytes, cudaStream_t stream)
+{
+  return run_sync(a, dir, aligned, comm, fused_ws_bytes, stream);
+}
+size_t sync_gather_bytes(uint32_t C, const AnodeSyncComm *comm) { return comm ? gather_bytes(C, (uint32_t)comm->world) : 0; }
+int sync_world(const AnodeSyncComm *comm) { return comm ? comm->world : 1; }
 
 }  // namespace anode_b200
 

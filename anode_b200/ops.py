@@ -550,6 +550,8 @@ class SyncBatchNormRelu(FusedBatchNormRelu):
     def launches_per_step(self):
         """Two kernels per step where a kernel with the exchange inside serves the shape; otherwise, per
         direction, reduce kernel, exchange (or merge) kernel and apply kernel."""
+        if self.comm.world == 1:
+            return 2
         if getattr(self.comm, "_exchange", None) is None:
             return 6
         if self._x is None:
@@ -559,23 +561,31 @@ class SyncBatchNormRelu(FusedBatchNormRelu):
         return sum(1 if kind(d0, c, n, d) != 4 else 3 for d in (0, 1))      # 4: the plain kernel (ANODE_KERNEL_PLAIN)
 
     def step_from_host(self, hx, hdy, hy, hdx, chunk_channels=0):
-        """This rank's shard in (page-locked) host memory: whole-shard copies around the two
-        synchronized kernels, all on the current stream (the single-GPU pipeline over channel blocks
-        is not used here: every block would be a collective of its own).  Returns 1."""
-        dev = self.mean.device
-        if self._dev is None or self._dev[0].shape != hx.shape:
-            self._dev = tuple(torch.empty(hx.shape, dtype=torch.float32, device=dev) for _ in range(3))
-        x, dy, y = self._dev
-        x.copy_(hx, non_blocking=True)
-        dy.copy_(hdy, non_blocking=True)
-        self.forward(x, out=y)
-        self.backward(dy, out=dy)              # dx over dy
-        hy.copy_(y, non_blocking=True)
-        hdx.copy_(dy, non_blocking=True)
-        return 1
+        """This rank's shard in (page-locked) host memory, through ONE C-ABI call: channel blocks copied in
+        and out on the library's copy streams while the synchronized kernels of the block in between run.
+        Returns the number of channel blocks (each is one synchronized forward and one backward)."""
+        for t in (hx, hdy, hy, hdx):
+            if t.is_cuda or not t.is_contiguous() or t.dtype != torch.float32:
+                raise ValueError("step_from_host takes contiguous float32 host tensors")
+        d0, c, n = dims_of(hx)
+        lib = _lib.load()
+        total = self.global_count if self.global_count is not None else d0 * n * self.comm.world
+        need = int(lib.anode_gpu_sync_batch_norm_host_step_staging_bytes(d0, c, n, total, self.comm.handle, int(chunk_channels)))
+        if need == 0:
+            raise AnodeError(-2, "anode_gpu_sync_batch_norm_host_step_staging_bytes")
+        if self._staging is None or self._staging.numel() < need:
+            self._staging = None
+            self._staging = torch.empty(need, dtype=torch.uint8, device=self.mean.device)
+        check(lib.anode_gpu_sync_batch_norm_relu_step_host_3d1_packed_f32(
+            d0, c, n, ctypes.c_uint64(total), ctypes.c_float(self.epsilon), ctypes.c_float(self.avg_rate), int(self.relu),
+            _hp(hx), _hp(hdy), _p(self.gamma), _p(self.beta), _hp(hy), _hp(hdx),
+            _p(self.mean), _p(self.var), _p(self.avg_mean), _p(self.avg_var), _p(self.dgamma), _p(self.dbeta),
+            self.comm.handle, ctypes.c_void_p(self._staging.data_ptr()), need, int(chunk_channels), _cfg(None), _stream(None)),
+            "anode_gpu_sync_batch_norm_relu_step_host_3d1_packed_f32")
+        return int(lib.anode_gpu_sync_batch_norm_host_step_blocks(d0, c, n, total, self.comm.handle, int(chunk_channels)))
 
     def host_step_status(self):
-        return self.status()
+        return FusedBatchNormRelu.host_step_status(self)
 
     def __init__(self, channels, comm=None, global_count=None, exchange=True, **kw):
         super().__init__(channels, **kw)

@@ -427,6 +427,25 @@ int anode_gpu_sync_batch_norm_relu_bwd_3d1_packed_f32(
     struct AnodeSyncComm *comm, void *workspace, size_t workspace_bytes,
     const struct KernelConfig *cfg, struct CUstream_st *stream);
 
+/* anode_gpu_batch_norm_relu_fused_step_host_3d1_packed_f32 for one rank's shard of a batch sharded over
+ * the ranks of `comm`: host tensors in, host tensors out, channel blocks travelling in both directions
+ * while the synchronized kernels of the block in between run.  Every rank cuts the layer into the same
+ * blocks (the default block size follows from global_count and the number of ranks; pass the same
+ * chunk_channels everywhere otherwise) and so makes the same sequence of synchronized launches.
+ * `staging` as in the one-GPU call, sized by anode_gpu_sync_batch_norm_host_step_staging_bytes. */
+size_t anode_gpu_sync_batch_norm_host_step_staging_bytes(uint32_t dim0, uint32_t dim1, uint32_t dim2, uint64_t global_count,
+                                                         struct AnodeSyncComm *comm, uint32_t chunk_channels);
+uint32_t anode_gpu_sync_batch_norm_host_step_blocks(uint32_t dim0, uint32_t dim1, uint32_t dim2, uint64_t global_count,
+                                                    struct AnodeSyncComm *comm, uint32_t chunk_channels);
+int anode_gpu_sync_batch_norm_relu_step_host_3d1_packed_f32(
+    uint32_t dim0, uint32_t dim1, uint32_t dim2, uint64_t global_count,
+    float epsilon, float avg_rate, int relu,
+    const float *host_x, const float *host_dy, const float *gamma, const float *beta,
+    float *host_y, float *host_dx,
+    float *mean, float *var, float *run_mean, float *run_var, float *dgamma, float *dbeta,
+    struct AnodeSyncComm *comm, void *staging, size_t staging_bytes, uint32_t chunk_channels,
+    const struct KernelConfig *cfg, struct CUstream_st *stream);
+
 /* The residual-block epilogue of anode_gpu_batch_norm_add_act_fused_{fwd,bwd}_3d1_packed_f32 with
  * statistics and backward sums over all ranks: y = act(bn(x) + residual) per shard (shortcut plus
  * normalized branch, then positive_clip: examples/run_imagenet_mpi.rs:191-195, 224-226, which the

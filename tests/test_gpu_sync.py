@@ -33,7 +33,7 @@ def _worker(rank, world, port, shape, axis, out_dir, dist_kind, exchange):
     dy = torch.from_numpy(np.ascontiguousarray(d["dy"][tuple(idx)])).cuda()
     per_channel = int(np.prod(shape)) // shape[1]          # shards may be uneven: the global count is stated
     layer = ops.SyncBatchNormRelu(shape[1], epsilon=1e-5, avg_rate=0.1, exchange=exchange, global_count=per_channel)
-    assert layer.launches_per_step == (2 if (exchange and world > 1) else 6)
+    assert layer.launches_per_step == (2 if (exchange or world == 1) else 6)
     layer.gamma.copy_(torch.from_numpy(d["gamma"])); layer.beta.copy_(torch.from_numpy(d["beta"]))
     # twice on one workspace, other data the first time: nothing of a step may reach the next one
     for xs, dys in ((x * 2.0 + 1.0, dy * 0.5), (x, dy)):
@@ -42,6 +42,15 @@ def _worker(rank, world, port, shape, axis, out_dir, dist_kind, exchange):
         dx = layer.backward(dys)
     torch.cuda.synchronize()
     assert layer.status() == 0
+    # the same step with the shard in page-locked host memory, through the one-call host-buffer entry point
+    hx, hdy = x.cpu().pin_memory(), dy.cpu().pin_memory()
+    hy, hdx = torch.empty_like(hx).pin_memory(), torch.empty_like(hx).pin_memory()
+    layer.avg_mean.zero_(); layer.avg_var.fill_(1.0)
+    blocks = layer.step_from_host(hx, hdy, hy, hdx, chunk_channels=max(1, shape[1] // 3))
+    torch.cuda.synchronize()
+    assert blocks >= 1 and layer.host_step_status() == 0
+    tol = lambda a, b: bool(((a - b).abs() <= 1e-5 + 1e-4 * b.abs()).all())
+    assert tol(hy, y.cpu()) and tol(hdx, dx.cpu()), "host-buffer step differs from the device step"
     # the gradient all-reduce that shares the communicator (SumSpmdOp's role)
     grad = torch.full((1000,), float(rank + 1), device="cuda")
     layer.comm.allreduce_sum(grad)
