@@ -378,10 +378,10 @@ def bench_workload(ops, name, rank, world, steps, warmup, dist, device, sample_c
     res = {"ms_per_step": ms, "fwd_ms": fwd, "bwd_ms": bwd, "elements_local": n_local, "elements_global": n_global,
            "value": n_global / (ms * 1e-3), "clocks": clocks, "launches_per_step": layer.launches_per_step, "parity": parity}
     if with_e2e:
+        res["e2e"] = bench_e2e(ops, layer, x, dy, y, dx, dist, device, min(steps, 3))     # first: it compares with y, dx of the timed steps
         res["infer"] = bench_infer(layer, x, y, steps, warmup)
         if world == 1:
             res["residual_block"] = bench_residual(ops, layer, x, dy, y, dx, steps, warmup)
-        res["e2e"] = bench_e2e(ops, layer, x, dy, y, dx, dist, device, min(steps, 3))
     return res
 
 
