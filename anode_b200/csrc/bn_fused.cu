@@ -119,10 +119,10 @@ static RingKernel pick_ring_kernel(const Plan &p, int dir, uint32_t &threads)
   (void)p;
   if (ring_warps(dir) == 16) {
     threads = ring16::kRingThreads;
-    return dir == 0 ? ring16::bn_ring_kernel<0, 0> : ring16::bn_ring_kernel<1, 0>;
+    return dir == 0 ? ring16::bn_ring_kernel<0> : ring16::bn_ring_kernel<1>;
   }
   threads = ring8::kRingThreads;
-  return dir == 0 ? ring8::bn_ring_kernel<0, 0> : ring8::bn_ring_kernel<1, 0>;
+  return dir == 0 ? ring8::bn_ring_kernel<0> : ring8::bn_ring_kernel<1>;
 }
 
 int launch_ring(FusedArgs &a, const RingGeom &g, int dir, cudaStream_t stream)

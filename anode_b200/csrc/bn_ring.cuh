@@ -19,8 +19,8 @@
 //                    precision (every block obtains bit-identical coefficients; with several
 //                    GPUs the owner block exchanges per-GPU records with the peers here) and
 //                    stages the visit's coefficients in a second mailbox.
-//                    (The split modes used with the NCCL exchange still count partials per unit
-//                    and publish per-channel records.)
+//                    (In the three-launch form of the synchronized calls the reduce launch still counts
+//                    partials per unit and the apply launch reads prepared coefficients.)
 //
 // Every wait is bounded: a wait that runs out sets a status bit, raises the block's abort flag
 // and all three roles drain and leave.
@@ -49,24 +49,6 @@ constexpr uint32_t kConsumers = ANODE_RING_CONSUMERS;   // consumer threads (a p
 constexpr uint32_t kRingThreads = kConsumers + 96;   // + producer, delivery and coefficient warps
 constexpr uint32_t kCopyBytes = ANODE_RING_COPY_BYTES;   // size of one bulk copy (a multiple of 16)
 constexpr long long kWaitCycles = 3000000000ll;      // about 1.5 s at 2 GHz
-
-// Optional per-block cycle accounting (build with -DANODE_RING_PROFILE): 16 counters per block are
-// written behind the regular workspace contents.
-#ifndef RING_PROF_DECL
-#ifdef ANODE_RING_PROFILE
-#define RING_PROF_DECL long long pf_t = clock64(); long long pf[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-#define RING_PROF(i) { const long long pf_n = clock64(); pf[i] += pf_n - pf_t; pf_t = pf_n; }
-#define RING_PROF_OUT(base) { unsigned long long *pf_o = reinterpret_cast<unsigned long long *>(a.ws + a.ws_capacity - (1u << 20)) + 24 * (size_t)blockIdx.x + (base); for (int pf_i = 0; pf_i < 8; ++pf_i) pf_o[pf_i] = (unsigned long long)pf[pf_i]; }
-__device__ __forceinline__ unsigned long long gtimer() { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
-// timeline samples: [0..4095] publish time per channel; then 4 values per apply visit of block 0
-#define RING_TL(idx, val) { reinterpret_cast<unsigned long long *>(a.ws + a.ws_capacity - 512 * 1024)[idx] = (val); }
-#else
-#define RING_PROF_DECL
-#define RING_PROF(i) {}
-#define RING_PROF_OUT(base) {}
-#define RING_TL(idx, val) {}
-#endif
-#endif   // RING_PROF_DECL
 
 struct RingCtl {
   unsigned long long full[kMaxSlots], empty[kMaxSlots];
@@ -207,7 +189,7 @@ __device__ __forceinline__ float4 *coef_box(unsigned char *sm, const RingGeom &g
 // ======================================================================================
 // consumer side
 // ======================================================================================
-// ---- regime R: each consumer warp handles vectors warp*32 + lane + i*256 of the tile ----------
+// ---- each consumer warp handles vectors warp*32 + lane + i*256 of the tile ----------
 constexpr uint32_t kCWarps = kConsumers / 32;
 constexpr uint32_t kPerTurn = 32 / kCWarps;      // mailbox entries the delivery warp merges per turn
 
@@ -231,16 +213,10 @@ __device__ __forceinline__ void warp_reduce_R(const FusedArgs &a, const RingGeom
   uint32_t ax = smem_u32(slot_x(sm, g, slot)) + tid * 16;
   if constexpr (DIR == 0) {
     // shifted sums (see bn_fused.cuh), two accumulator pairs
-#ifdef ANODE_RING_PROFILE
-    long long tq0 = clock64();
-#endif
     // K: the first element of the warp's share (lane 0 has the lowest vector index, so it has a
     // vector whenever any lane has one).  One shift per warp makes s and q plain sums over lanes.
     float K = cnt ? lds128(ax).v[0] : 0.f;
     K = __shfl_sync(0xffffffffu, K, 0);
-#ifdef ANODE_RING_PROFILE
-    long long tq1 = clock64();
-#endif
     float s0 = 0.f, q0 = 0.f, s1 = 0.f, q1 = 0.f;
     uint32_t i = 0;
     for (; i + 4 <= cnt; i += 4, ax += 4 * kVecStride) {
@@ -265,14 +241,8 @@ __device__ __forceinline__ void warp_reduce_R(const FusedArgs &a, const RingGeom
 #pragma unroll
       for (int e = 0; e < 4; ++e) { const float d0 = v0.v[e] - K; s0 += d0; q0 = fmaf(d0, d0, q0); }
     }
-#ifdef ANODE_RING_PROFILE
-    long long tq2 = clock64();
-#endif
     __syncwarp();
     if (lane == 0) mbar_arrive(&ctl->empty[slot]);
-#ifdef ANODE_RING_PROFILE
-    long long tq3 = clock64();
-#endif
     const float s = warp_sum(s0 + s1), q = warp_sum(q0 + q1);
     const uint32_t nw = __reduce_add_sync(0xffffffffu, cnt * 4);
     if (lane == 0) {
@@ -285,13 +255,6 @@ __device__ __forceinline__ void warp_reduce_R(const FusedArgs &a, const RingGeom
       }
       res[warp] = make_float4(m.n, m.mean, m.m2, 0.f);
     }
-#ifdef ANODE_RING_PROFILE
-    if (blockIdx.x == 0 && tid == 0) {
-      long long tq4 = clock64();
-      unsigned long long *dbg = reinterpret_cast<unsigned long long *>(a.ws + a.ws_capacity - 256 * 1024);
-      dbg[0] += tq1 - tq0; dbg[1] += tq2 - tq1; dbg[2] += tq3 - tq2; dbg[3] += tq4 - tq3; dbg[4] += 1; dbg[5] += cnt;
-    }
-#endif
   } else {
     uint32_t ad = ax + g.slot_floats * 4;
     const float4 cf = slot_side<1>(sm, g, slot)[0];
@@ -652,11 +615,11 @@ __device__ __forceinline__ bool pull_merge_unit(const FusedArgs &a, RingCtl *ctl
 // ======================================================================================
 // the kernel
 // ======================================================================================
-template <int DIR, int REGIME>
+// Whole-row tiles only (one channel per unit): short-row shapes are served by the cluster kernel
+// (bn_segres.cu) and the plain kernel.
+template <int DIR>
 __global__ void __launch_bounds__(kRingThreads, 1) bn_ring_kernel(const FusedArgs a, const RingGeom g)
 {
-  // Short-row shapes (regime S) are served by the cluster kernel (bn_segres.cu) and the plain kernel.
-  static_assert(REGIME == 0, "the warp-specialised kernel handles whole-row tiles only");
   extern __shared__ __align__(128) unsigned char sm[];
   RingCtl *ctl = reinterpret_cast<RingCtl *>(sm);
   const Plan &P = a.plan;
@@ -684,38 +647,24 @@ __global__ void __launch_bounds__(kRingThreads, 1) bn_ring_kernel(const FusedArg
     uint32_t nres = 0, ncoef = 0;             // reduce count, apply count
     uint32_t slot = g.slots - 1, par = 1;     // ring position, stepped without divisions
     TileRange tr;
-    RING_PROF_DECL
     while (sc.next_range(P, kind, tr)) {
       if (++slot == g.slots) { slot = 0; par ^= 1u; }
       if (kind == 0) {
         const uint32_t q = nres % kResQ, qpar = (nres / kResQ) & 1u; ++nres;
         // the partial mailbox entry must have been emptied by the delivery warp (first pass: free)
         bool ok = warp_wait(&ctl->res_empty[q], qpar ^ 1u, ctl, status, ANODE_ST_WAIT_STATS);
-        RING_PROF(0)
         ok = ok && warp_wait(&ctl->full[slot], par, ctl, status, ANODE_ST_WAIT_STATS);
-        RING_PROF(1)
         if (!ok) break;                                 // warps are independent: no barrier to honour
         warp_reduce_R<DIR>(a, g, sm, ctl, tr, slot, res_box(sm, g, q));
         if (lane == 0) mbar_arrive(&ctl->res_full[q]);
-        RING_PROF(3)
       } else {
         const uint32_t q = ncoef % kCoefQ, qpar = (ncoef / kCoefQ) & 1u; ++ncoef;
-#ifdef ANODE_RING_PROFILE
-        const unsigned long long tl_need = gtimer();
-#endif
         bool ok = warp_wait(&ctl->coef_full[q], qpar, ctl, status, ANODE_ST_WAIT_STATS);
-#ifdef ANODE_RING_PROFILE
-        if (blockIdx.x == 0 && tid == 0 && ncoef <= 256) { RING_TL(4096 + 4 * (ncoef - 1), tl_need) RING_TL(4096 + 4 * (ncoef - 1) + 1, gtimer()) RING_TL(4096 + 4 * (ncoef - 1) + 2, (unsigned long long)tr.unit) }
-#endif
-        RING_PROF(4)
         ok = ok && warp_wait(&ctl->full[slot], par, ctl, status, ANODE_ST_WAIT_STATS);
-        RING_PROF(5)
         if (!ok) break;
         warp_apply_R<DIR>(a, g, sm, ctl, tr, slot, coef_box(sm, g, P.cb, q), q);
-        RING_PROF(7)
       }
     }
-    if (tid == 0) RING_PROF_OUT(0)
   } else if (warp == kConsumers / 32) {
     // ------------------------------------------------------------------ producer
     const uint64_t keep = policy_keep(), drop = policy_drop();
@@ -724,14 +673,12 @@ __global__ void __launch_bounds__(kRingThreads, 1) bn_ring_kernel(const FusedArg
     uint32_t slot = g.slots - 1, par = 1;
     bool ok = true;
     TileRange tr;
-    RING_PROF_DECL
     while (ok && sc.next_range(P, kind, tr)) {
       ++k;
       if (++slot == g.slots) { slot = 0; par ^= 1u; }
       uint32_t okw = 1;
       if (lane == 0) okw = mbar_wait(&ctl->empty[slot], par ^ 1u, ctl, status, ANODE_ST_WAIT_STATS) ? 1u : 0u;
       ok = __shfl_sync(0xffffffffu, okw, 0) != 0;     // one lane decides for the warp
-      RING_PROF(0)
       if (!ok) { --k; break; }
       float *xs = slot_x(sm, g, slot);
       if (DIR == 1 && kind == 0) {
@@ -747,11 +694,7 @@ __global__ void __launch_bounds__(kRingThreads, 1) bn_ring_kernel(const FusedArg
       const uint32_t row_bytes = tr.len * 4u;
       if (lane == 0) mbar_arrive_expect_tx(&ctl->full[slot], row_bytes * tr.rows * (DIR == 1 ? 2u : 1u));
       __syncwarp();
-#ifdef ANODE_RING_NO_KEEP
-      const uint64_t pol = drop;
-#else
       const uint64_t pol = (kind == 0 && a.mode == MODE_FUSED) ? keep : drop;
-#endif
       // every row is fetched as several bulk copies (one per lane at a time), so that a tile made of
       // one long row still has many copies in flight
       const uint32_t per_row = (row_bytes + kCopyBytes - 1) / kCopyBytes, ncopies = per_row * tr.rows;
@@ -763,9 +706,7 @@ __global__ void __launch_bounds__(kRingThreads, 1) bn_ring_kernel(const FusedArg
         bulk_g2s(dst, a.x + goff, nb, &ctl->full[slot], pol);
         if (DIR == 1) bulk_g2s(dst + g.slot_floats, a.dy + goff, nb, &ctl->full[slot], pol);
       }
-      RING_PROF(1)
     }
-    if (lane == 0) RING_PROF_OUT(8)
     // after an abort: wait (bounded) for copies that were issued but will not be consumed
     if (!ok && lane == 0) {
       const uint32_t first = k > g.slots ? k - g.slots : 0;
@@ -780,22 +721,17 @@ __global__ void __launch_bounds__(kRingThreads, 1) bn_ring_kernel(const FusedArg
     // one lane per partial, so the fences and atomics of several tiles overlap.
     const uint32_t n_red = sc.do_reduce ? sc.my_tiles : 0;
     uint32_t nres = 0;
-    RING_PROF_DECL
     while (nres < n_red) {
       // sleep on the next entry's barrier (no polling loop competing with the consumers for issue
       // slots), then take along whatever else has arrived in the meantime
       if (!warp_wait(&ctl->res_full[nres % kResQ], (nres / kResQ) & 1u, ctl, status, ANODE_ST_WAIT_STATS)) break;
-#ifdef ANODE_RING_PROFILE
-      const unsigned long long tl_pick = gtimer();
-#endif
       const uint32_t jd = nres + lane;
       const bool d_ok = lane < kResQ && jd < n_red && mbar_test(&ctl->res_full[jd % kResQ], (jd / kResQ) & 1u);
       const uint32_t d_mask = __ballot_sync(0xffffffffu, d_ok);
       uint32_t nd = __ffs(~d_mask) - 1;                               // in order: leading run of ones
       if (nd > kPerTurn) nd = kPerTurn;
-      RING_PROF(0)
       if (nd) {
-        if constexpr (REGIME == 0) {
+        {
           // entry e is served by lanes 8e .. 8e+7: one warp partial each, merged in a fixed order
           const uint32_t e = lane / kCWarps, w = lane % kCWarps;
           float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -829,19 +765,9 @@ __global__ void __launch_bounds__(kRingThreads, 1) bn_ring_kernel(const FusedArg
             __syncwarp();
             if (lane < nd) mbar_arrive(&ctl->res_empty[(nres + lane) % kResQ]);
             nres += nd;
-            RING_PROF(1)
             continue;
           }
           if (e < nd && w == 0) __stcg(ws_f4(a, P.off_part) + (size_t)(sc.b + (nres + e) * sc.G), v);
-        } else {
-          for (uint32_t e = 0; e < nd; ++e) {
-            const uint32_t j = nres + e, t = sc.b + j * sc.G;
-            const uint32_t c0 = (t / P.tiles_per_unit) * P.cb;
-            const uint32_t cw = (P.C - c0 < P.cb) ? (P.C - c0) : P.cb;
-            const float4 *res = res_box(sm, g, j % kResQ);
-            float4 *part = ws_f4(a, P.off_part) + (size_t)t * P.cb;
-            for (uint32_t ci = lane; ci < cw; ci += 32) __stcg(part + ci, res[ci]);
-          }
         }
         __syncwarp();
         uint32_t last = 0, unit = 0;
@@ -856,39 +782,23 @@ __global__ void __launch_bounds__(kRingThreads, 1) bn_ring_kernel(const FusedArg
           last = (old + 1 == P.tiles_per_unit) ? 1u : 0u;
         }
         uint32_t lmask = __ballot_sync(0xffffffffu, last != 0);
-        RING_PROF(1)
-#ifdef ANODE_RING_PROFILE
-        const unsigned long long tl_atom = gtimer();
-#endif
         while (lmask) {
           const uint32_t src = __ffs(lmask) - 1; lmask &= lmask - 1;
           const uint32_t u = __shfl_sync(0xffffffffu, unit, src);
           warp_finish_unit_R<DIR>(a, u);
           if (lane == 0) done[u] = 0;
-#ifdef ANODE_RING_PROFILE
-          if (lane == 0) { RING_TL(u, gtimer()) RING_TL(8192 + 2 * u, tl_pick) RING_TL(8192 + 2 * u + 1, tl_atom) }
-#endif
-          RING_PROF(2)
         }
         nres += nd;
-#ifdef ANODE_RING_PROFILE
-        pf[4] += nd; pf[5] += 1;
-#endif
       }
     }
-    if (lane == 0) RING_PROF_OUT(16)
   } else {
     // ------------------------------------------------------------------ coefficient warp
-    // Apply visit j of this block is tile b + j*G.  Lane e looks after visit ncoef + e: it polls the
-    // tagged records of the visit's channels (zero = not ready yet) and, once all are there, the
-    // warp assembles (mean, scale, beta | B, C0) per channel into the visit's mailbox entry.
+    // Apply visit j of this block is tile b + j*G (one channel per unit).
     const uint32_t n_app = sc.do_apply ? sc.my_tiles : 0;
-    const unsigned long long *rec = reinterpret_cast<const unsigned long long *>(a.ws + P.off_rec);
     uint32_t ncoef = 0;
-    long long t_idle = clock64();
-    if (REGIME == 0 && a.mode == MODE_FUSED) {
-      // regime R, fused: merge each unit's partials here (see pull_merge_unit); consecutive visits of
-      // the same unit reuse the result
+    if (a.mode == MODE_FUSED) {
+      // merge each unit's partials here (see pull_merge_unit); consecutive visits of the same unit reuse
+      // the result
       uint32_t have = 0xffffffffu;
       float4 c0 = make_float4(0.f, 0.f, 0.f, 0.f), c1 = c0;
       while (ncoef < n_app) {
@@ -906,84 +816,18 @@ __global__ void __launch_bounds__(kRingThreads, 1) bn_ring_kernel(const FusedArg
         }
         ++ncoef;
       }
-      ncoef = n_app;      // skip the generic loop below
-    }
-    while (ncoef < n_app) {
-      if (!warp_wait(&ctl->coef_empty[ncoef % kCoefQ], ((ncoef / kCoefQ) & 1u) ^ 1u, ctl, status, ANODE_ST_WAIT_STATS)) break;
-      const uint32_t ja = ncoef + lane;
-      bool a_ok = lane < kCoefQ && ja < n_app && mbar_test(&ctl->coef_empty[ja % kCoefQ], ((ja / kCoefQ) & 1u) ^ 1u);
-      uint32_t c0 = 0, cw = 0;
-      unsigned long long r0 = 0;
-      float in_mean = 0.f, in_scale = 1.f, in_beta = 0.f;
-      if (a_ok) {
-        const uint32_t t = sc.b + ja * sc.G;
-        c0 = (t / P.tiles_per_unit) * P.cb;
-        cw = (P.C - c0 < P.cb) ? (P.C - c0) : P.cb;
-        if (a.mode == MODE_FUSED) {
-          if constexpr (REGIME == 0) {
-            // the inputs do not depend on the record: fetch them in the same round trip
-            const float gm = a.gamma ? a.gamma[c0] : 1.0f;
-            in_beta = (a.gamma && a.beta) ? a.beta[c0] : 0.0f;
-            if constexpr (DIR == 1) { in_mean = a.mean_in[c0]; in_scale = gm * inv_std(a.var_in[c0]); } else { in_scale = gm; }
-            r0 = ld_acquire_gpu_u64(rec + c0);
-            a_ok = r0 != 0ull;
-          } else {
-            for (uint32_t ci = 0; ci < cw && a_ok; ++ci) a_ok = ld_acquire_gpu_u64(rec + c0 + ci) != 0ull;
-          }
+    } else {
+      // apply pass of the three-launch form: the coefficients were prepared by the exchange / merge kernel
+      while (ncoef < n_app) {
+        if (!warp_wait(&ctl->coef_empty[ncoef % kCoefQ], ((ncoef / kCoefQ) & 1u) ^ 1u, ctl, status, ANODE_ST_WAIT_STATS)) break;
+        const uint32_t c = (sc.b + ncoef * sc.G) / P.tiles_per_unit;
+        if (lane == 0) {
+          const float4 *coef = ws_f4(a, P.off_coef) + 2 * (size_t)c;
+          float4 *box = coef_box(sm, g, P.cb, ncoef % kCoefQ);
+          box[0] = __ldcg(coef); box[1] = __ldcg(coef + 1);
+          mbar_arrive(&ctl->coef_full[ncoef % kCoefQ]);
         }
-      }
-      const uint32_t a_mask = __ballot_sync(0xffffffffu, a_ok);
-      const uint32_t na = __ffs(~a_mask) - 1;
-      if (__shfl_sync(0xffffffffu, (uint32_t)ctl->abort, 0)) break;
-      if (na) {
-        if (REGIME == 0 && a.mode == MODE_FUSED) {
-          // lane e completes entry e on its own from what it already holds
-          if (lane < na) {
-            float4 *box = coef_box(sm, g, P.cb, (ncoef + lane) % kCoefQ);
-            const float lo = __uint_as_float((uint32_t)(r0 & 0xffffffffull)), hi = __uint_as_float((uint32_t)(r0 >> 32));
-            if constexpr (DIR == 0) {
-              box[0] = make_float4(lo, in_scale * hi, in_beta, 0.f);            // (mean, gamma*rstd, beta)
-              box[1] = make_float4(0.f, 0.f, 0.f, 0.f);
-            } else {
-              box[0] = make_float4(in_mean, in_scale, in_beta, 0.f);
-              box[1] = make_float4(lo, hi, 0.f, 0.f);                           // (B, C0)
-            }
-          }
-        } else {
-          for (uint32_t e = 0; e < na; ++e) {
-            const uint32_t ec0 = __shfl_sync(0xffffffffu, c0, e), ecw = __shfl_sync(0xffffffffu, cw, e);
-            float4 *box = coef_box(sm, g, P.cb, (ncoef + e) % kCoefQ);
-            for (uint32_t ci = lane; ci < ecw; ci += 32) {
-              const uint32_t c = ec0 + ci;
-              if (a.mode != MODE_FUSED) {
-                // coefficients were prepared by a separate merge kernel
-                const float4 *coef = ws_f4(a, P.off_coef) + 2 * (size_t)c;
-                box[2 * ci] = __ldcg(coef); box[2 * ci + 1] = __ldcg(coef + 1);
-              } else {
-                const unsigned long long rv = ld_acquire_gpu_u64(rec + c);
-                const float lo = __uint_as_float((uint32_t)(rv & 0xffffffffull)), hi = __uint_as_float((uint32_t)(rv >> 32));
-                const float gm = a.gamma ? a.gamma[c] : 1.0f;
-                const float bt = (a.gamma && a.beta) ? a.beta[c] : 0.0f;
-                if constexpr (DIR == 0) {
-                  box[2 * ci] = make_float4(lo, gm * hi, bt, 0.f);
-                  box[2 * ci + 1] = make_float4(0.f, 0.f, 0.f, 0.f);
-                } else {
-                  box[2 * ci] = make_float4(a.mean_in[c], gm * inv_std(a.var_in[c]), bt, 0.f);
-                  box[2 * ci + 1] = make_float4(lo, hi, 0.f, 0.f);
-                }
-              }
-            }
-          }
-        }
-        __syncwarp();
-        if (lane < na) mbar_arrive(&ctl->coef_full[(ncoef + lane) % kCoefQ]);
-        ncoef += na;
-        t_idle = clock64();
-      } else {
-        __nanosleep(200);      // the unit is not complete yet: look again a little later
-        uint32_t give_up = 0;
-        if (lane == 0 && clock64() - t_idle > kWaitCycles) { atomicOr(status, ANODE_ST_WAIT_STATS); ctl->abort = 1; give_up = 1; }
-        if (__shfl_sync(0xffffffffu, give_up, 0)) break;
+        ++ncoef;
       }
     }
   }
@@ -1000,14 +844,9 @@ __global__ void __launch_bounds__(kRingThreads, 1) bn_ring_kernel(const FusedArg
       ctl->last_block = (atomicAdd(exit_ctr, 1u) + 1 == gridDim.x) ? 1u : 0u;
     }
     __syncthreads();
-    if (ctl->last_block) {
-      if constexpr (REGIME == 0) {
-        if (tid == 0) *ws_u32(a, 8) = ctl->parity ^ 1u;       // the next launch uses the other partial buffer
-      } else {
-        unsigned long long *rec = reinterpret_cast<unsigned long long *>(a.ws + P.off_rec);
-        for (uint32_t c = tid; c < P.C; c += kRingThreads) rec[c] = 0ull;
-      }
-      if (tid == 0) *exit_ctr = 0;
+    if (ctl->last_block && tid == 0) {
+      *ws_u32(a, 8) = ctl->parity ^ 1u;       // the next launch uses the other partial buffer
+      *exit_ctr = 0;
     }
   }
 }

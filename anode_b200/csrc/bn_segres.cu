@@ -47,7 +47,6 @@ struct SegGeom {
   uint32_t cluster;     // blocks per unit
   uint32_t rows;        // samples per block
   uint32_t units;
-  uint32_t stages;      // 1: one unit per cluster, several blocks per SM; 2: persistent, next unit's copies in flight
   uint32_t off_col, off_coef, off_part, off_stage, stage_bytes, off_dy, off_e, smem_bytes;   // off_e: residual (forward) / saved output (backward)
 };
 
@@ -67,11 +66,10 @@ __device__ __forceinline__ void st_sys_u64(unsigned long long *p, unsigned long 
   asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-__device__ __forceinline__ void cp_async_wait_but_one() { asm volatile("cp.async.wait_group 1;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
 
-// The cluster walks the units cid, cid + clusters, ... (with one stage the grid has a cluster per
-// unit and the loop runs once).  With two stages each block keeps two slices in shared memory: the
-// one being worked on and the next unit's, whose copies are in flight meanwhile.
+// The grid has one cluster per unit; a cluster launched with fewer clusters than units walks the
+// units cid, cid + clusters, ...
 template <int DIR>
 __global__ void __launch_bounds__(kSegThreads) bn_segres_kernel(const FusedArgs a, const SegGeom g)
 {
@@ -92,7 +90,8 @@ __global__ void __launch_bounds__(kSegThreads) bn_segres_kernel(const FusedArgs 
   float4 *parts = reinterpret_cast<float4 *>(sm + g.off_part);      // two buffers of one per channel
 
   // slice of unit u -> stage st, dense [rows][Lw]
-  auto issue = [&](uint32_t u, uint32_t st) {
+  auto issue = [&](uint32_t u) {
+    const uint32_t st = 0;
     const uint32_t c0 = u * g.cb, cw = (C - c0 < g.cb) ? (C - c0) : g.cb;
     const uint32_t L4 = cw * dim0 / 4;
     float *sx = reinterpret_cast<float *>(sm + g.off_stage + (size_t)st * g.stage_bytes);
@@ -117,11 +116,10 @@ __global__ void __launch_bounds__(kSegThreads) bn_segres_kernel(const FusedArgs 
     }
   };
 
-  if (cid < g.units) issue(cid, 0);
-  cp_async_commit();
-  uint32_t j = 0;
-  for (uint32_t u = cid; u < g.units; u += ncl, ++j) {
-    const uint32_t st = g.stages == 2 ? (j & 1u) : 0u;
+  for (uint32_t u = cid; u < g.units; u += ncl) {
+    const uint32_t st = 0;
+    issue(u);
+    cp_async_commit();
     const uint32_t c0 = u * g.cb, cw = (C - c0 < g.cb) ? (C - c0) : g.cb;
     const uint32_t Lw = cw * dim0, L4 = Lw / 4;                     // floats / float4s per sample in this unit
     const float *sx = reinterpret_cast<const float *>(sm + g.off_stage + (size_t)st * g.stage_bytes);
@@ -130,9 +128,6 @@ __global__ void __launch_bounds__(kSegThreads) bn_segres_kernel(const FusedArgs 
     const bool has_e = (DIR == 0 ? a.res : a.ymask) != nullptr;
     float4 *part = parts + (size_t)st * g.cb;
 
-    // the next unit's slice starts travelling now (its stage was released at the end of the last round)
-    if (g.stages == 2 && u + ncl < g.units) issue(u + ncl, st ^ 1u);
-    cp_async_commit();
     if (DIR == 1) {
       // what the mask needs is known before the sums: (mean, gamma*rstd, beta)
       for (uint32_t ci = tid; ci < cw; ci += kSegThreads) {
@@ -143,7 +138,7 @@ __global__ void __launch_bounds__(kSegThreads) bn_segres_kernel(const FusedArgs 
         coef[8 * ci + 2] = (a.gamma && a.beta) ? a.beta[c] : 0.0f;
       }
     }
-    cp_async_wait_but_one();          // everything but the copies issued just above has landed
+    cp_async_wait_all();              // the slice has landed
     __syncthreads();
 
     // ---- per-column sums.  Thread (grp, v): float4 column v, samples grp, grp+G, ...
@@ -389,10 +384,9 @@ static bool seg_geom(uint32_t dim0, uint32_t C, uint32_t N, int dir, bool extra,
   g.off_coef = 2 * kSegColFloats * 4;
   g.off_part = g.off_coef + (uint32_t)align_up_u64((uint64_t)cb * 32, 16);
   g.off_stage = g.off_part + (uint32_t)align_up_u64((uint64_t)2 * cb * 16, 128);
-  // `stages` stages of `tensors` slices each; a slice is padded to 128 bytes
-  g.stages = 1;
-  if (g.off_stage + (uint64_t)g.stages * tensors * ((uint64_t)L * 4 + 128) > budget) return false;
-  const uint32_t rows_max = (uint32_t)(((budget - g.off_stage) / (g.stages * tensors) - 128) / (L * 4));
+  // `tensors` slices, each padded to 128 bytes
+  if (g.off_stage + (uint64_t)tensors * ((uint64_t)L * 4 + 128) > budget) return false;
+  const uint32_t rows_max = (uint32_t)(((budget - g.off_stage) / tensors - 128) / (L * 4));
   uint32_t cl = 1;
   while (cl < kSegMaxCluster && (uint64_t)cl * rows_max < N) cl *= 2;
   if ((uint64_t)cl * rows_max < N) return false;
@@ -402,7 +396,7 @@ static bool seg_geom(uint32_t dim0, uint32_t C, uint32_t N, int dir, bool extra,
   g.off_dy = slice;                         // within a stage: x, then dy (backward), then the extra tensor
   g.off_e = (dir == 1 ? 2u : 1u) * slice;
   g.stage_bytes = tensors * slice;
-  g.smem_bytes = g.off_stage + g.stages * g.stage_bytes;
+  g.smem_bytes = g.off_stage + g.stage_bytes;
   return g.smem_bytes <= budget;
 }
 
@@ -464,9 +458,7 @@ int launch_segres(FusedArgs &a, int dir, cudaStream_t stream)
     fit = it->second;
   }
   if (fit <= 0) return ANODE_E_LAUNCH;
-  // two stages: as many clusters as are resident at once walk the units; one stage: a cluster per unit
-  const uint32_t clusters = (g.stages == 2 && (uint32_t)fit < g.units) ? (uint32_t)fit : g.units;
-  cfg.gridDim = dim3(clusters * g.cluster);
+  cfg.gridDim = dim3(g.units * g.cluster);
   if (cudaLaunchKernelEx(&cfg, kernel, a, g) != cudaSuccess) { (void)cudaGetLastError(); return ANODE_E_LAUNCH; }
   return ANODE_OK;
 }

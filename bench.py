@@ -39,11 +39,24 @@ WORKLOADS = {
     "cfg5_wide": dict(shape=(1024, 2048, 7, 7), dist="student3", loc=0.0, scale=4.0, axis=0),
 }
 DEFAULT = "cfg3_syncbn"
-# DRAM bytes per element (ncu dram__bytes_read.sum + dram__bytes_write.sum per launch / elements),
-# captured on a 16-channel case of the same per-channel geometry and scaled by elements (the
-# kernels stream channel by channel, so traffic is proportional to the channel count).
-TRAFFIC = {"cfg3_syncbn": {"fwd": 8.78, "bwd": 16.22}}
-TRAFFIC_SOURCE = "profiles/bn_ring_kernels_cfg3_syncbn.md section 3"
+# DRAM bytes per element of the default workload's kernels come from the ncu summary under profiles/
+# (row "traffic per element" of its counter table: dram__bytes_read.sum + dram__bytes_write.sum per launch
+# / elements, captured on a 16-channel case of the same per-channel geometry; the kernels work channel by
+# channel, so traffic is proportional to the channel count and is scaled by elements here).
+TRAFFIC_SOURCE = "profiles/bn_ring_kernels_cfg3_syncbn.md"
+
+
+def measured_traffic():
+    """{'fwd': bytes/element, 'bwd': bytes/element} of the default workload on one GPU, or {}."""
+    import re
+    try:
+        text = open(os.path.join(ROOT, TRAFFIC_SOURCE)).read()
+    except OSError:
+        return {}
+    m = re.search(r"^\|\s*traffic per element[^|]*\|\s*([0-9.]+)\s*B[^|]*\|\s*([0-9.]+)\s*B", text, flags=re.M)
+    return {"fwd": float(m.group(1)), "bwd": float(m.group(2))} if m else {}
+
+
 SEED = 20240607
 BLOCKS = 8        # the global tensor is generated in 8 blocks along the sharded axis, whatever N is
 
@@ -493,6 +506,8 @@ def main():
     ap.add_argument("--shape", default=None, help="custom global shape N,C,spatial... (N(0,1) data, sharded on axis 0); "
                     "used for small profiler captures")
     ap.add_argument("--no-extras", action="store_true", help="skip cpu_baseline, e2e and other_workloads")
+    ap.add_argument("--kernel", default="auto", choices=["auto", "tiled", "cluster", "resident", "plain"],
+                    help="kernel preference of the fused calls (anode_gpu_batch_norm_fused_set_kernel); for profiler captures")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.shape:
@@ -520,6 +535,7 @@ def main():
         tdist.init_process_group("nccl", device_id=device)
         dist = tdist
 
+    ops.set_kernel(args.kernel)
     main_res = bench_workload(ops, args.workload, rank, world, args.steps, args.warmup, dist, device,
                               sample_clocks=True, with_e2e=not args.no_extras)
     peak, peak_kind = hbm_peak()
@@ -567,11 +583,11 @@ def main():
         line["infer"] = main_res["infer"]
     if "residual_block" in main_res:
         line["residual_block"] = main_res["residual_block"]
-    tr = TRAFFIC.get(args.workload if world == 1 else "%s@%d" % (args.workload, world), {})
+    tr = measured_traffic() if (world == 1 and args.workload == DEFAULT and args.kernel == "auto") else {}
     for key, rk in (("bwd", "roofline"), ("fwd", "roofline_fwd")):
         if key in tr:
             line[rk]["traffic"] = tr[key] * main_res["elements_local"]
-            line[rk]["traffic_source"] = TRAFFIC_SOURCE
+            line[rk]["traffic_source"] = TRAFFIC_SOURCE + " (16-channel capture, scaled by elements)"
 
     if world == 1 and not args.no_extras:
         others = {}
