@@ -16,11 +16,14 @@
 namespace anode_b200 {
 
 // ---- planner constants, from sweeps on B200 -------------------------------------------------------
+#ifndef ANODE_SLACK_STEPS
+#define ANODE_SLACK_STEPS 2
+#endif
 const Tunables &tunables()
 {
   static const Tunables t = {
       32768,    // tile_floats
-      2,        // slack_steps
+      ANODE_SLACK_STEPS,        // slack_steps
       4,        // blocks_per_sm
       3,        // ring_slots
       4,        // ring_slots_bwd
