@@ -210,4 +210,126 @@ class FusedBatchNormRelu {
   size_t staging_bytes_ = 0;
 };
 
+// Communicator of the synchronized entry points (one process per GPU).  `from_unique_id` wraps
+// anode_gpu_sync_comm_create (NCCL behind it; the 128-byte id comes from rank 0 by any means, in anode over
+// DistProcGroup, src/proc_mpi.rs:27-105); `exchange_only` has no NCCL and works once the world's exchange
+// buffers are attached.
+class SyncComm {
+ public:
+  static SyncComm from_unique_id(const void *id, int rank, int world)
+  {
+    SyncComm c; c.rank_ = rank; c.world_ = world;
+    check(anode_gpu_sync_comm_create(id, rank, world, &c.h_), "anode_gpu_sync_comm_create");
+    return c;
+  }
+  static SyncComm exchange_only(int rank, int world)
+  {
+    SyncComm c; c.rank_ = rank; c.world_ = world;
+    check(anode_gpu_sync_comm_create_exchange_only(rank, world, &c.h_), "anode_gpu_sync_comm_create_exchange_only");
+    return c;
+  }
+  // peer_ptrs[r]: rank r's exchange buffer as mapped into this process (anode_gpu_sync_exchange_bytes each, zeroed once)
+  void attach_exchange(void *const *peer_ptrs, uint32_t max_channels)
+  {
+    check(anode_gpu_sync_comm_attach_exchange(h_, peer_ptrs, max_channels), "anode_gpu_sync_comm_attach_exchange");
+  }
+  // SumSpmdOp's role for gradients (src/ops_gpu.rs:538-545), on the device
+  void allreduce_sum(DeviceArray &buf, cudaStream_t s = 0)
+  {
+    check(anode_gpu_sync_allreduce_sum_f32(h_, buf.ptr(), buf.len(), raw(s)), "anode_gpu_sync_allreduce_sum_f32");
+  }
+  AnodeSyncComm *handle() const { return h_; }
+  int rank() const { return rank_; }
+  int world() const { return world_; }
+  SyncComm(SyncComm &&o) noexcept : h_(o.h_), rank_(o.rank_), world_(o.world_) { o.h_ = nullptr; }
+  SyncComm &operator=(SyncComm &&o) noexcept { if (this != &o) { reset(); h_ = o.h_; rank_ = o.rank_; world_ = o.world_; o.h_ = nullptr; } return *this; }
+  SyncComm(const SyncComm &) = delete;
+  SyncComm &operator=(const SyncComm &) = delete;
+  ~SyncComm() { reset(); }
+
+ private:
+  SyncComm() = default;
+  void reset() { if (h_) { (void)anode_gpu_sync_comm_destroy(h_); h_ = nullptr; } }
+  AnodeSyncComm *h_ = nullptr;
+  int rank_ = 0, world_ = 1;
+};
+
+// FusedBatchNormRelu over a batch sharded across the ranks of a SyncComm: statistics, running averages,
+// dgamma and dbeta are those of the global batch (identical on every rank).  `global_count` is the number
+// of elements per channel over all ranks (the M of the formulas); 0 means equal shards.
+class SyncBatchNormRelu {
+ public:
+  SyncBatchNormRelu(SyncComm &comm, uint32_t channels, uint64_t global_count = 0, float epsilon = 1e-5f, float avg_rate = 0.1f,
+                    bool affine = true, bool relu = true)
+      : avg_mean(DeviceArray::zeros({channels})), avg_var(DeviceArray::filled({channels}, 1.0f)),
+        mean(DeviceArray::zeros({channels})), var(DeviceArray::zeros({channels})),
+        comm_(comm), global_count_(global_count), epsilon_(epsilon), avg_rate_(avg_rate), relu_(relu)
+  {
+    if (affine) {
+      gamma = DeviceArray::filled({channels}, 1.0f); beta = DeviceArray::zeros({channels});
+      dgamma = DeviceArray::zeros({channels}); dbeta = DeviceArray::zeros({channels});
+    }
+  }
+  void forward(const DeviceArray &x, DeviceArray &y, cudaStream_t s = 0)
+  {
+    const Dims d = dims_of(x, leading_axes(x));
+    want_len(y, x.len(), "y");
+    workspace_for(d, s);
+    check(anode_gpu_sync_batch_norm_relu_fwd_3d1_packed_f32(d.dim0, d.dim1, d.dim2, epsilon_, avg_rate_, relu_ ? 1 : 0, x.ptr(), opt(&gamma),
+                                                            opt(&beta), y.ptr(), mean.ptr(), var.ptr(), avg_mean.ptr(), avg_var.ptr(),
+                                                            comm_.handle(), ws_, ws_bytes_, kernel_config(), raw(s)),
+          "anode_gpu_sync_batch_norm_relu_fwd_3d1_packed_f32");
+    x_ = &x;
+  }
+  void backward(const DeviceArray &dy, DeviceArray &dx, WriteCap cap = WriteCap::Assign, cudaStream_t s = 0)
+  {
+    if (!x_) throw Error(ANODE_E_NULL, "backward before forward");
+    const Dims d = dims_of(*x_, leading_axes(*x_));
+    want_len(dx, x_->len(), "dx");
+    const uint64_t total = global_count_ ? global_count_ : (uint64_t)d.dim0 * d.dim2 * (uint64_t)comm_.world();
+    check(anode_gpu_sync_batch_norm_relu_bwd_3d1_packed_f32(d.dim0, d.dim1, d.dim2, total, relu_ ? 1 : 0, cap == WriteCap::Accumulate ? 1 : 0,
+                                                            dy.ptr(), x_->ptr(), mean.ptr(), var.ptr(), opt(&gamma), opt(&beta), dx.ptr(),
+                                                            opt(&dgamma), opt(&dbeta), comm_.handle(), ws_, ws_bytes_, kernel_config(), raw(s)),
+          "anode_gpu_sync_batch_norm_relu_bwd_3d1_packed_f32");
+  }
+  uint32_t status(cudaStream_t s = 0) const
+  {
+    uint32_t st = 0;
+    if (ws_) check(anode_gpu_batch_norm_fused_status(ws_, raw(s), &st), "anode_gpu_batch_norm_fused_status");
+    return st;
+  }
+  ~SyncBatchNormRelu() { if (ws_) (void)cudaFree(ws_); }
+  SyncBatchNormRelu(const SyncBatchNormRelu &) = delete;
+  SyncBatchNormRelu &operator=(const SyncBatchNormRelu &) = delete;
+
+  DeviceArray gamma, beta, avg_mean, avg_var, mean, var, dgamma, dbeta;
+
+ private:
+  static std::vector<int> leading_axes(const DeviceArray &x)
+  {
+    std::vector<int> a;
+    for (size_t i = 0; i + 2 < x.size().size(); ++i) a.push_back((int)i);
+    return a;
+  }
+  // a workspace belongs to one problem: a new shape gets a fresh, zeroed one
+  void workspace_for(Dims d, cudaStream_t s)
+  {
+    if (ws_ && d.dim0 == dims_.dim0 && d.dim1 == dims_.dim1 && d.dim2 == dims_.dim2) return;
+    if (ws_) { (void)cudaFree(ws_); ws_ = nullptr; }
+    ws_bytes_ = anode_gpu_sync_batch_norm_workspace_bytes(d.dim0, d.dim1, d.dim2, comm_.world());
+    if (ws_bytes_ == 0) throw Error(ANODE_E_DIMS, "anode_gpu_sync_batch_norm_workspace_bytes");
+    cuda_check(cudaMalloc(&ws_, ws_bytes_), "cudaMalloc");
+    check(anode_gpu_batch_norm_fused_workspace_init(ws_, ws_bytes_, raw(s)), "anode_gpu_batch_norm_fused_workspace_init");
+    dims_ = d;
+  }
+  SyncComm &comm_;
+  uint64_t global_count_;
+  float epsilon_, avg_rate_;
+  bool relu_;
+  void *ws_ = nullptr;
+  size_t ws_bytes_ = 0;
+  Dims dims_{};
+  const DeviceArray *x_ = nullptr;
+};
+
 }  // namespace anode

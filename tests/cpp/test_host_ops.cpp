@@ -246,6 +246,39 @@ static void test_error_behaviour()
   cudaFree(ws);
 }
 
+// The synchronized layer with a communicator of one rank gives what the one-GPU layer gives; the handle
+// without NCCL refuses what it cannot do (several ranks need several GPUs: tests/test_gpu_sync.py).
+static void test_sync_layer_world_one()
+{
+  const Problem p = make_problem({28, 28, 12, 6}, 41, 0.5, 2.0);
+  const Truth t = truth_f64(p, true);
+  SyncComm comm = SyncComm::exchange_only(0, 1);
+  SyncBatchNormRelu layer(comm, p.c);
+  layer.gamma.copy_from_host(p.gamma.data()); layer.beta.copy_from_host(p.beta.data());
+  DeviceArray x = DeviceArray::from_host(p.size, p.x.data()), dy = DeviceArray::from_host(p.size, p.dy.data());
+  DeviceArray y(p.size), dx(p.size);
+  for (int rep = 0; rep < 2; ++rep) {          // twice on one workspace
+    layer.avg_mean = DeviceArray::zeros({p.c}); layer.avg_var = DeviceArray::filled({p.c}, 1.0f);
+    layer.forward(x, y);
+    layer.backward(dy, dx);
+  }
+  EXPECT(layer.status() == 0, "status word");
+  expect_close(y.to_host(), t.y, "sync y", &t.borderline);
+  expect_close(dx.to_host(), t.dx, "sync dx", &t.borderline);
+  expect_close(layer.mean.to_host(), t.mean, "sync mean");
+  expect_close(layer.var.to_host(), t.var, "sync var");
+  expect_close(layer.avg_mean.to_host(), t.run_mean, "sync avg_mean");
+  expect_close(layer.avg_var.to_host(), t.run_var, "sync avg_var");
+  expect_sum_close(layer.dgamma.to_host(), t.dgamma, "sync dgamma");
+  expect_sum_close(layer.dbeta.to_host(), t.dbeta, "sync dbeta");
+  // two claimed ranks, no exchange attached, no NCCL: refused before anything is enqueued
+  SyncComm two = SyncComm::exchange_only(0, 2);
+  SyncBatchNormRelu orphan(two, p.c);
+  bool refused = false;
+  try { orphan.forward(x, y); } catch (const Error &e) { refused = e.code == ANODE_E_COMM; }
+  EXPECT(refused, "a communicator without NCCL and without an exchange buffer refuses the call");
+}
+
 int main()
 {
   int devs = 0;
@@ -257,6 +290,7 @@ int main()
       {"inference_branch", test_inference_branch},
       {"host_step_equals_resident_calls", test_host_step_equals_resident_calls},
       {"error_behaviour", test_error_behaviour},
+      {"sync_layer_world_one", test_sync_layer_world_one},
   };
   int failed = 0;
   for (const auto &t : tests) {
