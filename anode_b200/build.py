@@ -68,8 +68,11 @@ def build_library(force=False, verbose=False):
         if p.returncode:
             raise RuntimeError("nvcc failed on %s" % s)
     # the CUDA runtime is linked statically (nvcc's default); NCCL is looked up with dlopen
-    link = [nvcc, "-shared", "-o", LIB] + objs + ["-gencode", "arch=compute_100a,code=sm_100a", "-Xlinker", "-Bsymbolic", "-ldl"]
+    # link to a temporary name and rename: a reader (or a copy of the tree) never sees a half-written library
+    tmp = LIB + ".tmp%d" % os.getpid()
+    link = [nvcc, "-shared", "-o", tmp] + objs + ["-gencode", "arch=compute_100a,code=sm_100a", "-Xlinker", "-Bsymbolic", "-ldl"]
     subprocess.check_call(link)
+    os.replace(tmp, LIB)
     return LIB
 
 

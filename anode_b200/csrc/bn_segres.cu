@@ -360,7 +360,13 @@ __global__ void __launch_bounds__(kSegThreads) bn_segres_kernel(const FusedArgs 
 // other's arithmetic.  (A persistent variant with two slices per block was measured slower: what
 // limits this kernel is the chain of short dependent phases per unit, which co-resident blocks overlap
 // better.)
-constexpr uint32_t kSegBlocksPerSm = 2;
+#ifndef ANODE_SEG_BPS_FWD
+#define ANODE_SEG_BPS_FWD 2
+#endif
+#ifndef ANODE_SEG_BPS_BWD
+#define ANODE_SEG_BPS_BWD 2
+#endif
+constexpr uint32_t kSegBlocksPerSmFwd = ANODE_SEG_BPS_FWD, kSegBlocksPerSmBwd = ANODE_SEG_BPS_BWD;
 constexpr uint32_t kSegLongRowCluster = 4;      // long aligned rows are taken when a channel fits this many blocks
 
 // Geometry for direction `dir`, or false when this kernel does not apply: the shape is not a
@@ -377,7 +383,7 @@ static bool seg_geom(uint32_t dim0, uint32_t C, uint32_t N, int dir, bool extra,
   if (cb >= C) cb = C;
   if ((uint64_t)cb * dim0 > 4 * kSegThreads || (cb * dim0) % 4 != 0) return false;
   const uint32_t L = cb * dim0, tensors = (dir == 1 ? 2u : 1u) + (extra ? 1u : 0u);
-  const uint32_t per_block = (228u * 1024u) / kSegBlocksPerSm - 1024u;       // what one of k co-resident blocks may use
+  const uint32_t per_block = (228u * 1024u) / (dir == 0 ? kSegBlocksPerSmFwd : kSegBlocksPerSmBwd) - 1024u;       // what one of k co-resident blocks may use
   const uint32_t budget = per_block > 227u * 1024u ? 227u * 1024u : per_block;
   g.cb = cb; g.units = ceil_div_u32(C, cb);
   g.off_col = 0;
