@@ -157,7 +157,6 @@ int launch_ring(FusedArgs &a, const RingGeom &g, int dir, cudaStream_t stream)
     a.plan.lookahead_steps = ceil_div_u32(a.plan.tiles_per_unit, a.plan.grid) + tunables().slack_steps;
   }
   a.use_rec = a.mode == MODE_FUSED ? 1u : 0u;
-  { const char *e = getenv("ANODE_B200_DYNAMIC"); a.dynamic = (e && atoi(e)) ? 1u : 0u; }
   void *params[] = {(void *)&a, (void *)&g};
   cudaError_t e;
   if (a.mode == MODE_FUSED)

@@ -52,7 +52,6 @@ struct FusedArgs {
   uint32_t rank, world, epoch, xchg_channels;
   unsigned long long *xchg[8];
   long long wait_cycles;   // bound of every in-kernel wait, in SM clock cycles
-  uint32_t dynamic;        // tiled kernel, fused mode: blocks take tiles from two counters instead of a fixed share
 };
 
 // 1/sqrt(v) as every kernel here computes it (IEEE divide and square root), so that the

@@ -50,23 +50,14 @@ constexpr uint32_t kRingThreads = kConsumers + 96;   // + producer, delivery and
 constexpr uint32_t kCopyBytes = ANODE_RING_COPY_BYTES;   // size of one bulk copy (a multiple of 16)
 constexpr long long kWaitCycles = 3000000000ll;      // about 1.5 s at 2 GHz
 
-constexpr uint32_t kAppQ = 16;               // apply visits the producer may be ahead of the coefficient warp
-constexpr uint32_t kDescEnd = 0xffffffffu;      // slot descriptor: no more visits
-constexpr uint32_t kOffRedCtr = 64, kOffAppCtr = 128;   // the two hand-out counters, in the workspace header (a line each)
 struct RingCtl {
   unsigned long long full[kMaxSlots], empty[kMaxSlots];
   unsigned long long res_full[kResQ], res_empty[kResQ];
   unsigned long long coef_full[kCoefQ], coef_empty[kCoefQ];
-  unsigned long long app_full[kAppQ];     // dynamic hand-out: apply visit j's tile number is in app_tile[j % kAppQ]
   float mom[3 * (kConsumers / 32)];
   volatile uint32_t abort;
   uint32_t last_block;
   uint32_t parity;       // which of the two tagged-partial buffers this launch uses
-  // dynamic hand-out of tiles (see the kernel): what each slot holds, the tile of each mailbox entry, the
-  // tiles of the apply visits issued so far, and how far the producer has got
-  uint32_t desc[kMaxSlots];
-  uint32_t res_tile[kResQ];
-  uint32_t app_tile[kAppQ];
 };
 static_assert(sizeof(RingCtl) <= kRingCtlBytes, "RingCtl outgrew the room reserved for it");
 
@@ -641,7 +632,6 @@ __global__ void __launch_bounds__(kRingThreads, 1) bn_ring_kernel(const FusedArg
     for (uint32_t i = 0; i < g.slots; ++i) { mbar_init(&ctl->full[i], 1); mbar_init(&ctl->empty[i], kCWarps); }
     for (uint32_t i = 0; i < kResQ; ++i) { mbar_init(&ctl->res_full[i], kCWarps); mbar_init(&ctl->res_empty[i], 1); }
     for (uint32_t i = 0; i < kCoefQ; ++i) { mbar_init(&ctl->coef_full[i], 1); mbar_init(&ctl->coef_empty[i], kCWarps); }
-    for (uint32_t i = 0; i < kAppQ; ++i) mbar_init(&ctl->app_full[i], 1);
     ctl->abort = 0; ctl->last_block = 0;
     ctl->parity = *ws_u32(a, 8) & 1u;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -651,40 +641,8 @@ __global__ void __launch_bounds__(kRingThreads, 1) bn_ring_kernel(const FusedArg
 
   Sched sc; sc.init(a);
   uint32_t kind;
-  // Dynamic hand-out (fused mode): instead of the fixed tiles b, b+G, ... a block takes the next tile to
-  // reduce and the next tile to apply from two counters in the workspace, so that blocks that get ahead
-  // do more and nobody waits for a straggler's fixed share.  The producer draws the numbers and tells the
-  // other roles through the slot descriptors.
-  const bool dyn = a.dynamic != 0 && a.mode == MODE_FUSED;
 
-  if (warp < kConsumers / 32 && dyn) {
-    // ------------------------------------------------------------------ consumers, dynamic hand-out
-    uint32_t nres = 0, ncoef = 0;
-    uint32_t slot = g.slots - 1, par = 1;
-    for (;;) {
-      if (++slot == g.slots) { slot = 0; par ^= 1u; }
-      if (!warp_wait(&ctl->full[slot], par, ctl, status, ANODE_ST_WAIT_STATS)) break;
-      const uint32_t d = ctl->desc[slot];
-      if (d == kDescEnd) {
-        // pass the end mark on to the delivery warp, in the order of the partials
-        const uint32_t q = nres % kResQ, qpar = (nres / kResQ) & 1u;
-        if (!warp_wait(&ctl->res_empty[q], qpar ^ 1u, ctl, status, ANODE_ST_WAIT_STATS)) break;
-        if (lane == 0) { if (warp == 0) ctl->res_tile[q] = kDescEnd; mbar_arrive(&ctl->res_full[q]); }
-        break;
-      }
-      const TileRange tr = tile_range(P, d & 0x7fffffffu);
-      if ((d >> 31) == 0) {
-        const uint32_t q = nres % kResQ, qpar = (nres / kResQ) & 1u; ++nres;
-        if (!warp_wait(&ctl->res_empty[q], qpar ^ 1u, ctl, status, ANODE_ST_WAIT_STATS)) break;
-        warp_reduce_R<DIR>(a, g, sm, ctl, tr, slot, res_box(sm, g, q));
-        if (lane == 0) { if (warp == 0) ctl->res_tile[q] = d; mbar_arrive(&ctl->res_full[q]); }
-      } else {
-        const uint32_t q = ncoef % kCoefQ, qpar = (ncoef / kCoefQ) & 1u; ++ncoef;
-        if (!warp_wait(&ctl->coef_full[q], qpar, ctl, status, ANODE_ST_WAIT_STATS)) break;
-        warp_apply_R<DIR>(a, g, sm, ctl, tr, slot, coef_box(sm, g, P.cb, q), q);
-      }
-    }
-  } else if (warp < kConsumers / 32) {
+  if (warp < kConsumers / 32) {
     // ------------------------------------------------------------------ consumers
     uint32_t nres = 0, ncoef = 0;             // reduce count, apply count
     uint32_t slot = g.slots - 1, par = 1;     // ring position, stepped without divisions
@@ -714,30 +672,41 @@ __global__ void __launch_bounds__(kRingThreads, 1) bn_ring_kernel(const FusedArg
     uint32_t k = 0;
     uint32_t slot = g.slots - 1, par = 1;
     bool ok = true;
-    TileRange tr{};
-    // issues the copies of one visit into the next slot; `desc` is what the other roles read in dynamic mode
-    auto issue = [&](uint32_t kind, const TileRange &tr, uint32_t desc) {
+    TileRange tr;
+    // backward pass: (mean, gamma / std, beta) of the current channel and, fetched ahead, of the next one
+    uint32_t side_c = 0xffffffffu, next_c = 0xffffffffu, next_age = 0;
+    float4 side_v = make_float4(0.f, 0.f, 0.f, 0.f), next_v = side_v, next_raw = side_v;
+    bool next_pending = false;
+    auto load_side_raw = [&](uint32_t c) {      // the loads only; the arithmetic waits until the values are used
+      float4 r = make_float4(0.f, 1.f, 1.f, 0.f);
+      if constexpr (DIR == 1) {
+        r.x = a.mean_in[c]; r.y = a.var_in[c];
+        r.z = a.gamma ? a.gamma[c] : 1.0f;
+        r.w = (a.gamma && a.beta) ? a.beta[c] : 0.0f;
+      }
+      return r;
+    };
+    auto finish_side = [&](const float4 &r) { return make_float4(r.x, r.z * inv_std(r.y), r.w, 0.f); };
+    while (ok && sc.next_range(P, kind, tr)) {
       ++k;
       if (++slot == g.slots) { slot = 0; par ^= 1u; }
       uint32_t okw = 1;
       if (lane == 0) okw = mbar_wait(&ctl->empty[slot], par ^ 1u, ctl, status, ANODE_ST_WAIT_STATS) ? 1u : 0u;
       ok = __shfl_sync(0xffffffffu, okw, 0) != 0;     // one lane decides for the warp
-      if (!ok) { --k; return; }
-      if (lane == 0) ctl->desc[slot] = desc;
-      if (desc == kDescEnd) {                          // nothing to copy: the consumers stop at this slot
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&ctl->full[slot]);
-        return;
-      }
+      if (!ok) { --k; break; }
       float *xs = slot_x(sm, g, slot);
       if (DIR == 1 && kind == 0) {
-        // coefficients of the reduce visit's ReLU mask, per channel of the unit
-        float4 *side = slot_side<1>(sm, g, slot);
-        for (uint32_t ci = lane; ci < tr.cw; ci += 32) {
-          const uint32_t c = tr.c0 + ci;
-          const float gm = a.gamma ? a.gamma[c] : 1.0f;
-          side[ci] = make_float4(a.mean_in[c], gm * inv_std(a.var_in[c]), (a.gamma && a.beta) ? a.beta[c] : 0.0f, 0.f);
+        // coefficients of the reduce visit's ReLU mask (one channel per unit here).  They change only when the
+        // block moves on to another channel, and the next channel's are fetched ahead of time: a visit's issue
+        // must not wait for global memory, or the slot stays empty for that long.
+        if (tr.c0 != side_c) {
+          if (tr.c0 == next_c) side_v = next_pending ? finish_side(next_raw) : next_v;
+          else side_v = finish_side(load_side_raw(tr.c0));
+          side_c = tr.c0;
+          next_c = tr.c0 + 1 < P.C ? tr.c0 + 1 : tr.c0;
+          next_raw = load_side_raw(next_c); next_pending = true; next_age = 0;
         }
+        if (lane == 0) slot_side<1>(sm, g, slot)[0] = side_v;
       }
       __syncwarp();
       const uint32_t row_bytes = tr.len * 4u;
@@ -755,56 +724,8 @@ __global__ void __launch_bounds__(kRingThreads, 1) bn_ring_kernel(const FusedArg
         bulk_g2s(dst, a.x + goff, nb, &ctl->full[slot], pol);
         if (DIR == 1) bulk_g2s(dst + g.slot_floats, a.dy + goff, nb, &ctl->full[slot], pol);
       }
-    };
-    if (!dyn) {
-      while (ok && sc.next_range(P, kind, tr)) issue(kind, tr, 0);
-    } else {
-      // Hand-out rule that keeps the blocks from waiting on one another in a cycle: a tile is taken for its
-      // apply visit only once every tile of its unit has been taken for its reduce visit, and nothing is
-      // taken for a reduce visit between that check and the apply visit's issue.  Then a block that waits for
-      // a unit's statistics never sits on an unreduced tile of that unit or of a lower one.
-      uint32_t *red_ctr = ws_u32(a, kOffRedCtr), *app_ctr = ws_u32(a, kOffAppCtr);
-      const uint32_t total = P.total_tiles, look = P.lookahead_steps, none = 0xffffffffu;
-      bool red_left = true, app_left = true;
-      uint32_t red_seen = 0;                 // a lower bound of the reduce counter
-      uint32_t pend = none;                  // tile taken for its apply visit and not issued yet
-      uint32_t napp = 0;
-      auto publish = [&](uint32_t t) {       // tells the coefficient warp the tile of apply visit napp
-        if (lane == 0) { ctl->app_tile[napp % kAppQ] = t; mbar_arrive(&ctl->app_full[napp % kAppQ]); }
-        ++napp;
-      };
-      for (uint32_t s = 0; ok && (red_left || app_left || pend != none); ++s) {
-        if (red_left) {
-          uint32_t r = 0;
-          if (lane == 0) r = atomicAdd(red_ctr, 1u);
-          r = __shfl_sync(0xffffffffu, r, 0);
-          if (r >= total) { red_left = false; red_seen = total; }
-          else { red_seen = r + 1; issue(0, tile_range(P, r), r); if (!ok) break; }
-        }
-        if (pend == none && app_left && (s >= look || !red_left)) {
-          uint32_t t = 0;
-          if (lane == 0) t = atomicAdd(app_ctr, 1u);
-          t = __shfl_sync(0xffffffffu, t, 0);
-          if (t >= total) app_left = false; else pend = t;
-        }
-        if (pend != none) {
-          // while tiles of the unit are still untaken this block keeps taking tiles to reduce (above) instead
-          // of waiting: the counter then moves whatever the other blocks do
-          const uint32_t unit_end = (pend / P.tiles_per_unit + 1) * P.tiles_per_unit;
-          if (red_seen < unit_end) {
-            uint32_t v = 0;
-            if (lane == 0) v = ld_relaxed_gpu(red_ctr);
-            v = __shfl_sync(0xffffffffu, v, 0);
-            if (v > red_seen) red_seen = v;
-          }
-          if (red_seen >= unit_end) {
-            publish(pend);
-            issue(1, tile_range(P, pend), pend | 0x80000000u);
-            pend = none;
-          }
-        }
-      }
-      if (ok) { publish(kDescEnd); issue(0, tr, kDescEnd); }
+      // the values fetched ahead are turned into coefficients one visit later, when they have arrived
+      if (DIR == 1 && next_pending && next_age++ >= 1) { next_v = finish_side(next_raw); next_pending = false; }
     }
     // after an abort: wait (bounded) for copies that were issued but will not be consumed
     if (!ok && lane == 0) {
@@ -818,50 +739,8 @@ __global__ void __launch_bounds__(kRingThreads, 1) bn_ring_kernel(const FusedArg
     // ------------------------------------------------------------------ delivery warp
     // Reduce visit j of this block is tile b + j*G.  Each turn serves every partial that waits,
     // one lane per partial, so the fences and atomics of several tiles overlap.
-    const uint32_t n_red = dyn ? 0 : (sc.do_reduce ? sc.my_tiles : 0);
+    const uint32_t n_red = sc.do_reduce ? sc.my_tiles : 0;
     uint32_t nres = 0;
-    // dynamic hand-out: the tile of each partial comes with it, and an end mark closes the sequence
-    for (bool end = false; dyn && !end;) {
-      if (!warp_wait(&ctl->res_full[nres % kResQ], (nres / kResQ) & 1u, ctl, status, ANODE_ST_WAIT_STATS)) break;
-      const uint32_t jd = nres + lane;
-      const bool d_ok = lane < kResQ && mbar_test(&ctl->res_full[jd % kResQ], (jd / kResQ) & 1u);
-      const uint32_t is_end = d_ok && ctl->res_tile[jd % kResQ] == kDescEnd;
-      uint32_t d_mask = __ballot_sync(0xffffffffu, d_ok);
-      const uint32_t e_mask = __ballot_sync(0xffffffffu, is_end);
-      uint32_t nd = __ffs(~d_mask) - 1;                               // in order: leading run of ones
-      if (e_mask && (uint32_t)(__ffs(e_mask) - 1) < nd) { nd = __ffs(e_mask) - 1; end = true; }
-      if (nd > kPerTurn) { nd = kPerTurn; end = false; }
-      const uint32_t e = lane / kCWarps, w = lane % kCWarps;
-      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (e < nd) v = res_box(sm, g, (nres + e) % kResQ)[w];
-      if constexpr (DIR == 0) {
-        Moments m{v.x, v.y, v.z};
-#pragma unroll
-        for (int o = (int)kCWarps / 2; o > 0; o >>= 1) {
-          Moments c;
-          c.n = __shfl_down_sync(0xffffffffu, m.n, o, kCWarps);
-          c.mean = __shfl_down_sync(0xffffffffu, m.mean, o, kCWarps);
-          c.m2 = __shfl_down_sync(0xffffffffu, m.m2, o, kCWarps);
-          m = merge(m, c);
-        }
-        v = make_float4(m.n, m.mean, m.m2, 0.f);
-      } else {
-#pragma unroll
-        for (int o = (int)kCWarps / 2; o > 0; o >>= 1) {
-          v.x += __shfl_down_sync(0xffffffffu, v.x, o, kCWarps);
-          v.y += __shfl_down_sync(0xffffffffu, v.y, o, kCWarps);
-        }
-      }
-      if (e < nd && w == 0) {
-        const size_t t = ctl->res_tile[(nres + e) % kResQ];
-        const float lo = DIR == 0 ? v.y : v.x, hi = DIR == 0 ? v.z : v.y;
-        st_relaxed_gpu_u64(tag_buf(a, ctl->parity) + t, pack_rec(lo, __uint_as_float(__float_as_uint(hi) | 1u)));
-        tag_buf(a, ctl->parity ^ 1u)[t] = 0ull;
-      }
-      __syncwarp();
-      if (lane < nd) mbar_arrive(&ctl->res_empty[(nres + lane) % kResQ]);
-      nres += nd;
-    }
     while (nres < n_red) {
       // sleep on the next entry's barrier (no polling loop competing with the consumers for issue
       // slots), then take along whatever else has arrived in the meantime
@@ -937,28 +816,7 @@ __global__ void __launch_bounds__(kRingThreads, 1) bn_ring_kernel(const FusedArg
     // Apply visit j of this block is tile b + j*G (one channel per unit).
     const uint32_t n_app = sc.do_apply ? sc.my_tiles : 0;
     uint32_t ncoef = 0;
-    if (dyn) {
-      uint32_t have = 0xffffffffu;
-      float4 c0 = make_float4(0.f, 0.f, 0.f, 0.f), c1 = c0;
-      for (;;) {
-        if (!warp_wait(&ctl->app_full[ncoef % kAppQ], (ncoef / kAppQ) & 1u, ctl, status, ANODE_ST_WAIT_STATS)) break;
-        const uint32_t t = ctl->app_tile[ncoef % kAppQ];
-        if (t == kDescEnd) break;
-        if (!warp_wait(&ctl->coef_empty[ncoef % kCoefQ], ((ncoef / kCoefQ) & 1u) ^ 1u, ctl, status, ANODE_ST_WAIT_STATS)) break;
-        const uint32_t u = t / P.tiles_per_unit;
-        if (u != have) {
-          // the block that applies the unit's first tile also writes the per-channel outputs
-          if (!pull_merge_unit<DIR>(a, ctl, status, u, t == u * P.tiles_per_unit, c0, c1)) break;
-          have = u;
-        }
-        if (lane == 0) {
-          float4 *box = coef_box(sm, g, P.cb, ncoef % kCoefQ);
-          box[0] = c0; box[1] = c1;
-          mbar_arrive(&ctl->coef_full[ncoef % kCoefQ]);
-        }
-        ++ncoef;
-      }
-    } else if (a.mode == MODE_FUSED) {
+    if (a.mode == MODE_FUSED) {
       // merge each unit's partials here (see pull_merge_unit); consecutive visits of the same unit reuse
       // the result
       uint32_t have = 0xffffffffu;
@@ -1009,7 +867,6 @@ __global__ void __launch_bounds__(kRingThreads, 1) bn_ring_kernel(const FusedArg
     if (ctl->last_block && tid == 0) {
       *ws_u32(a, 8) = ctl->parity ^ 1u;       // the next launch uses the other partial buffer
       *exit_ctr = 0;
-      *ws_u32(a, kOffRedCtr) = 0; *ws_u32(a, kOffAppCtr) = 0;
     }
   }
 }
