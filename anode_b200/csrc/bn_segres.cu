@@ -65,6 +65,8 @@ __device__ __forceinline__ void st_sys_u64(unsigned long long *p, unsigned long 
 {
   asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
 }
+// n / d for n < 65536 (see fast_div): the multiplier, computed once per thread
+__device__ __forceinline__ uint32_t seg_div_mul(uint32_t d) { return d > 1 ? 0xffffffffu / d + 1u : 0u; }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
 
@@ -77,7 +79,8 @@ __global__ void __launch_bounds__(kSegThreads) bn_segres_kernel(const FusedArgs 
   cg::cluster_group cluster = cg::this_cluster();
   const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const uint32_t rank = cluster.block_rank();
-  const uint32_t cid = blockIdx.x / g.cluster, ncl = gridDim.x / g.cluster;
+  const uint32_t csh = (uint32_t)__ffs((int)g.cluster) - 1u;        // the cluster size is a power of two
+  const uint32_t cid = blockIdx.x >> csh, ncl = gridDim.x >> csh;
   const uint32_t dim0 = a.plan.dim0, C = a.plan.C, N = a.plan.N;
   const uint32_t n0 = rank * g.rows;
   const uint32_t rows = n0 < N ? ((N - n0 < g.rows) ? (N - n0) : g.rows) : 0;
@@ -99,9 +102,10 @@ __global__ void __launch_bounds__(kSegThreads) bn_segres_kernel(const FusedArgs 
     float *se = reinterpret_cast<float *>(sm + g.off_stage + (size_t)st * g.stage_bytes + g.off_e);
     const float *extra = DIR == 0 ? a.res : a.ymask;       // residual epilogue: third (second) tensor of the slice
     const uint32_t total4 = rows * L4;
-    const uint32_t row = tid / L4;
+    const uint32_t mul = seg_div_mul(L4);
+    const uint32_t row = fast_div(tid, mul);
     uint32_t col = tid - row * L4;
-    const uint32_t drow = kSegThreads / L4, dcol = kSegThreads - drow * L4;
+    const uint32_t drow = fast_div(kSegThreads, mul), dcol = kSegThreads - drow * L4;
     // float offset of this thread's next piece; advancing by kSegThreads pieces moves drow samples
     // down and dcol pieces right, wrapping into the next sample
     size_t off = (size_t)n0 * rs + (size_t)c0 * dim0 + (size_t)row * rs + 4 * (size_t)col;
@@ -142,12 +146,13 @@ __global__ void __launch_bounds__(kSegThreads) bn_segres_kernel(const FusedArgs 
     __syncthreads();
 
     // ---- per-column sums.  Thread (grp, v): float4 column v, samples grp, grp+G, ...
-    const uint32_t G = kSegThreads / L4;                              // >= 1: L4 <= kSegThreads by construction
-    const uint32_t grp = tid / L4, v = tid - grp * L4;
+    const uint32_t mul_l4 = seg_div_mul(L4), mul_d0 = seg_div_mul(dim0);    // divisions by multiplication from here on
+    const uint32_t G = fast_div(kSegThreads, mul_l4);                  // >= 1: L4 <= kSegThreads by construction
+    const uint32_t grp = fast_div(tid, mul_l4), v = tid - grp * L4;
     const bool active = grp < G;
     uint32_t ch[4];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) ch[i] = active ? (4 * v + i) / dim0 : 0;
+    for (int i = 0; i < 4; ++i) ch[i] = active ? fast_div(4 * v + i, mul_d0) : 0;
     if (active) {
       const float *px = sx + 4 * (size_t)v;
       if (DIR == 0) {
@@ -200,14 +205,16 @@ __global__ void __launch_bounds__(kSegThreads) bn_segres_kernel(const FusedArgs 
     // every column has seen all `rows` samples).  Moments travel as (n, n*mean, M2 + n*mean^2):
     // plain sums in f64, which lose nothing that f32 inputs could have carried.
     const uint32_t Gr = G < rows ? G : rows;
+    const uint32_t mul_g = seg_div_mul(G);
+    const double inv_rows = rows ? 1.0 / (double)rows : 0.0;
     for (uint32_t col = tid; col < Lw; col += kSegThreads) {
       if (DIR == 0) {
         double t1 = 0.0, t2 = 0.0;
         for (uint32_t gi = 0; gi < Gr; ++gi) {
-          const double n = (double)((rows - gi + G - 1) / G), m = (double)colA[gi * Lw + col];
+          const double n = (double)fast_div(rows - gi + G - 1, mul_g), m = (double)colA[gi * Lw + col];
           t1 = fma(n, m, t1); t2 += (double)colB[gi * Lw + col] + n * m * m;
         }
-        const double mean = rows ? t1 / (double)rows : 0.0;
+        const double mean = t1 * inv_rows;
         colA[col] = (float)mean; colB[col] = (float)fmax(t2 - t1 * mean, 0.0);
       } else {
         double t1 = 0.0, t2 = 0.0;
@@ -235,7 +242,18 @@ __global__ void __launch_bounds__(kSegThreads) bn_segres_kernel(const FusedArgs 
     }
     cluster.sync();
 
-    // ---- merge the cluster's partials in rank order; every block computes the same coefficients
+    // ---- fetch the cluster's partials: one remote read per thread, all in flight together, instead of one
+    // thread per channel reading rank after rank.  The column arrays are free by now.
+    float4 *gath = reinterpret_cast<float4 *>(colA);                   // [channel][rank]
+    const bool gathered = cw * g.cluster <= 2 * kSegColFloats / 4;
+    if (gathered) {
+      for (uint32_t t = tid; t < cw * g.cluster; t += kSegThreads) {
+        const uint32_t ci = t >> csh, r = t & (g.cluster - 1u);
+        gath[t] = *cluster.map_shared_rank(part + ci, r);
+      }
+      __syncthreads();
+    }
+    // ---- merge them in rank order; every block computes the same coefficients
     for (uint32_t ci = tid; ci < cw; ci += kSegThreads) {
       const uint32_t c = c0 + ci;
       const float gm = a.gamma ? a.gamma[c] : 1.0f;
@@ -243,7 +261,7 @@ __global__ void __launch_bounds__(kSegThreads) bn_segres_kernel(const FusedArgs 
       double t0 = 0.0, t1 = 0.0, t2 = 0.0;
 #pragma unroll 4
       for (uint32_t r = 0; r < g.cluster; ++r) {
-        const float4 p = *cluster.map_shared_rank(part + ci, r);
+        const float4 p = gathered ? gath[ci * g.cluster + r] : *cluster.map_shared_rank(part + ci, r);
         if (DIR == 0) { const double n = (double)p.x, m = (double)p.y; t0 += n; t1 = fma(n, m, t1); t2 += (double)p.z + n * m * m; }
         else { t1 += (double)p.x; t2 += (double)p.y; }
       }
@@ -309,6 +327,9 @@ __global__ void __launch_bounds__(kSegThreads) bn_segres_kernel(const FusedArgs 
       }
     }
     __syncthreads();
+    // This block has read its neighbours' partials: say so now and collect everybody's word at the end of the
+    // unit (nobody may overwrite its partials or leave while a neighbour still reads them); the wait is then free.
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
 
     // ---- apply from shared memory, stream the result out
     if (active) {
@@ -349,9 +370,9 @@ __global__ void __launch_bounds__(kSegThreads) bn_segres_kernel(const FusedArgs 
         if (DIR == 1 && pr) __stcs(reinterpret_cast<float4 *>(pr + (size_t)r * rs), make_float4(dzs[0], dzs[1], dzs[2], dzs[3]));
       }
     }
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
     __syncthreads();      // this stage, the column arrays and the coefficients may be reused
   }
-  cluster.sync();         // nobody leaves while a neighbour may still read its partials
 }
 
 // ---- host side -------------------------------------------------------------------------------
