@@ -83,3 +83,45 @@ def check_layer(got, truth, x, gamma, beta, what="", atol_elem=ATOL, check_sums=
     if gamma is not None and check_sums:
         assert_sum_close(got["dgamma"], truth["dgamma"], what + "dgamma")
         assert_sum_close(got["dbeta"], truth["dbeta"], what + "dbeta")
+
+
+def check_layer_own_mask(d, got, what="", eps=1e-5):
+    """Compares a fused layer's outputs with a float64 computation that takes the layer's OWN ReLU decisions
+    (y > 0) wherever the pre-activation lies within 1e-5 of zero, and insists on the exact decision everywhere
+    else.  Unlike check_layer it can therefore hold dgamma, dbeta and dx to the usual tolerance on any input:
+    one undecidable mask moves the two sums by |dy| and, through them, every dx of the channel.
+    Returns the number of decisions that differ from the float64 ones."""
+    x = d["x"].astype(np.float64)
+    dy = d["dy"].astype(np.float64)
+    c = x.shape[1]
+    ax = (0,) + tuple(range(2, x.ndim))
+    bs = (1, c) + (1,) * (x.ndim - 2)
+    m = x.size // c
+    g = np.ones(c) if d["gamma"] is None else d["gamma"].astype(np.float64)
+    b = np.zeros(c) if d["gamma"] is None else d["beta"].astype(np.float64)
+    mean = x.mean(axis=ax)
+    var = x.var(axis=ax) + eps
+    r = 1.0 / np.sqrt(var)
+    xhat = (x - mean.reshape(bs)) * r.reshape(bs)
+    ybn = xhat * g.reshape(bs) + b.reshape(bs)
+    mask = got["y"] > 0
+    flips = mask != (ybn > 0)
+    assert not (flips & (np.abs(ybn) >= 1e-5)).any(), what + "a ReLU decision differs away from zero"
+    assert_close(got["mean"], mean, what + "mean")
+    assert_close(got["var"], var, what + "var")
+    assert_close(got["y"], ybn * mask, what + "y")
+    dz = dy * mask
+    s1 = dz.sum(axis=ax)
+    s2 = (dz * xhat).sum(axis=ax)
+    dx = (g * r).reshape(bs) * (dz - s1.reshape(bs) / m - xhat * s2.reshape(bs) / m)
+    # conditioning, not the kernel: the backward pass works from the f32 mean, which moves xhat by half an ulp of
+    # |mean| over sigma; and dx is a sum of f32 terms of the size of gamma/sigma * |dz|
+    cond = float(np.max(np.abs(mean) * r)) * 2e-7
+    mag = float(np.max(np.abs(g * r))) * float(np.max(np.abs(dz))) * 1.2e-7
+    assert_close(got["dx"], dx, what + "dx", atol=ATOL + cond + mag)
+    if d["gamma"] is not None:
+        rms1 = float(np.sqrt(np.mean(s1 * s1)))
+        rms2 = float(np.sqrt(np.mean(s2 * s2)))
+        assert_close(got["dbeta"], s1, what + "dbeta", atol=ATOL + RTOL * rms1)
+        assert_close(got["dgamma"], s2, what + "dgamma", atol=ATOL + RTOL * rms2 + cond * float(np.abs(dz).sum(axis=ax).max()))
+    return int(flips.sum())
