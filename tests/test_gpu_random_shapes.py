@@ -4,8 +4,9 @@ and the input gradient are held to the usual tolerance on inputs nobody picked b
 odd channel counts, one to a few hundred samples, means of several sigma."""
 import numpy as np
 import pytest
+import torch
 
-from tests.test_gpu_fused import run_fused
+from tests.test_gpu_fused import dev, host, run_fused
 from tests.util import check_layer_own_mask, make_inputs
 
 pytestmark = pytest.mark.gpu
@@ -52,3 +53,39 @@ def test_random_shapes_every_kernel(seed):
     finally:
         ops.set_kernel("auto")
     assert flips < 50
+
+
+def run_add_act(ops, d, res_h, slope):
+    """y = act(bn(x) + shortcut) and its adjoint through the operator interface."""
+    x = dev(d["x"]); dy = dev(d["dy"]); res = dev(res_h); g = dev(d["gamma"]); b = dev(d["beta"])
+    c = x.shape[1]
+    axes = list(range(x.dim() - 2))
+    mean = torch.zeros(c, device="cuda"); var = torch.zeros(c, device="cuda")
+    rm = dev(d["run_mean"]); rv = dev(d["run_var"])
+    dg = torch.zeros(c, device="cuda") if g is not None else None
+    db = torch.zeros(c, device="cuda") if g is not None else None
+    y = torch.full_like(x, float("nan")); dx = torch.full_like(x, float("nan")); dres = torch.full_like(x, float("nan"))
+    ws = ops.Workspace(*ops.dims_of(x), x.device)
+    ops.BatchNormalize2dAddActFusedOp.apply(axes, 1e-5, 0.1, x, res, y, mean, var, rm, rv, g, b, slope, ws)
+    ops.BatchNormalize2dAddActFusedOp.adjoint(axes, dy, x, y, mean, var, dx, dres, g, b, dg, db, slope, workspace=ws)
+    assert ws.status() == 0
+    return dict(y=host(y), dx=host(dx), dresidual=host(dres), mean=host(mean), var=host(var), dgamma=host(dg), dbeta=host(db))
+
+
+@pytest.mark.parametrize("seed", [21, 22])
+def test_random_shapes_residual_epilogue(seed):
+    from anode_b200 import ops
+    rng = np.random.default_rng(seed)
+    try:
+        for _ in range(30):
+            shape = random_case(rng)
+            d = make_inputs(shape, seed=int(rng.integers(1, 1 << 30)), loc=float(rng.choice([0.0, 0.5, 3.0])),
+                            scale=float(rng.choice([1.0, 2.0, 0.5])), affine=bool(rng.integers(0, 2)))
+            res_h = np.random.default_rng(int(rng.integers(1, 1 << 30))).standard_normal(shape).astype(np.float32)
+            slope = float(rng.choice([0.0, 0.0, 0.1]))
+            kernel = str(rng.choice(["auto", "cluster", "resident", "plain"]))
+            ops.set_kernel(kernel)
+            got = run_add_act(ops, d, res_h, slope)
+            check_layer_own_mask(d, got, "%r %s slope %g " % (shape, kernel, slope), residual=res_h, slope=slope)
+    finally:
+        ops.set_kernel("auto")

@@ -85,11 +85,13 @@ def check_layer(got, truth, x, gamma, beta, what="", atol_elem=ATOL, check_sums=
         assert_sum_close(got["dbeta"], truth["dbeta"], what + "dbeta")
 
 
-def check_layer_own_mask(d, got, what="", eps=1e-5):
+def check_layer_own_mask(d, got, what="", eps=1e-5, residual=None, slope=0.0):
     """Compares a fused layer's outputs with a float64 computation that takes the layer's OWN ReLU decisions
     (y > 0) wherever the pre-activation lies within 1e-5 of zero, and insists on the exact decision everywhere
     else.  Unlike check_layer it can therefore hold dgamma, dbeta and dx to the usual tolerance on any input:
     one undecidable mask moves the two sums by |dy| and, through them, every dx of the channel.
+    `residual` is the shortcut tensor of the residual epilogue (y = act(bn(x) + residual); got["dresidual"] is
+    checked when present), `slope` the activation's slope below zero (> 0 or exactly 0).
     Returns the number of decisions that differ from the float64 ones."""
     x = d["x"].astype(np.float64)
     dy = d["dy"].astype(np.float64)
@@ -104,13 +106,18 @@ def check_layer_own_mask(d, got, what="", eps=1e-5):
     r = 1.0 / np.sqrt(var)
     xhat = (x - mean.reshape(bs)) * r.reshape(bs)
     ybn = xhat * g.reshape(bs) + b.reshape(bs)
+    if residual is not None:
+        ybn = ybn + residual.astype(np.float64)
     mask = got["y"] > 0
     flips = mask != (ybn > 0)
     assert not (flips & (np.abs(ybn) >= 1e-5)).any(), what + "a ReLU decision differs away from zero"
     assert_close(got["mean"], mean, what + "mean")
     assert_close(got["var"], var, what + "var")
-    assert_close(got["y"], ybn * mask, what + "y")
-    dz = dy * mask
+    act = np.where(mask, 1.0, slope)
+    assert_close(got["y"], ybn * act, what + "y")
+    dz = dy * act
+    if got.get("dresidual") is not None:
+        assert_close(got["dresidual"], dz, what + "dresidual")
     s1 = dz.sum(axis=ax)
     s2 = (dz * xhat).sum(axis=ax)
     dx = (g * r).reshape(bs) * (dz - s1.reshape(bs) / m - xhat * s2.reshape(bs) / m)
