@@ -4,7 +4,7 @@ import numpy as np
 import pytest
 import torch
 
-from tests.util import assert_close, make_inputs
+from tests.util import assert_close, make_inputs, random_shapes
 
 pytestmark = pytest.mark.gpu
 
@@ -27,7 +27,7 @@ def truth(x, mean, var, gamma, beta, slope):
     ((2, 4, 16, 32, 32), 1.0, False),      # NCDHW, no activation, no affine
     ((1, 1, 1, 1), 0.0, False),
     ((3, 70000, 1, 1), 0.01, True),        # dim0 = 1: every element its own channel
-])
+] + [(s, [0.0, 0.1, 1.0][i % 3], i % 2 == 0) for i, s in enumerate(random_shapes(32, 12, max_elems=1e6))])
 def test_infer_matches_float64(shape, slope, affine):
     from anode_b200 import ops
     d = make_inputs(shape, seed=3, loc=0.5, scale=2.0, affine=affine)

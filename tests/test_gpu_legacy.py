@@ -5,12 +5,12 @@ import pytest
 import torch
 
 from oracle import bn_oracle as o
-from tests.util import assert_close, assert_sum_close, make_inputs
+from tests.util import assert_close, assert_sum_close, make_inputs, random_shapes
 
 pytestmark = pytest.mark.gpu
 
 SHAPES = [(32, 64, 28, 28), (5, 3, 7, 7), (3, 2, 1, 1), (2, 4, 3, 6, 8), (7, 5, 9, 13), (1, 1, 1, 1),
-          (64, 40, 7, 7), (2, 3, 64, 66)]
+          (64, 40, 7, 7), (2, 3, 64, 66)] + random_shapes(31, 12, max_elems=4e5)      # and a dozen nobody picked by hand
 
 
 def dev(a):

@@ -7,30 +7,11 @@ import pytest
 import torch
 
 from tests.test_gpu_fused import dev, host, run_fused
-from tests.util import check_layer_own_mask, make_inputs
+from tests.util import check_layer_own_mask, make_inputs, random_case
 
 pytestmark = pytest.mark.gpu
 
 KERNELS = ["auto", "tiled", "cluster", "resident", "plain"]
-
-
-def random_case(rng):
-    mode = int(rng.integers(0, 4))
-    nd = int(rng.choice([1, 2, 2, 3]))
-    if mode == 0:
-        sp = [int(rng.integers(1, 9)) for _ in range(nd)]                  # tiny rows
-    elif mode == 1:
-        sp = [int(rng.integers(1, 40)) for _ in range(nd)]
-    elif mode == 2:
-        sp = [int(rng.choice([7, 14, 28, 56, 112, 8, 16, 32, 64]))] * 2      # the networks' feature maps
-    else:
-        sp = [int(rng.integers(1, 6)), int(rng.integers(50, 3000))]         # long, mostly unaligned rows
-    dim0 = int(np.prod(sp))
-    c = int(rng.choice([1, 2, 3, 4, 5, 8, 16, 31, 64, 96, 130, 260]))
-    n = int(min(max(1, int(3e6 // (dim0 * c))), rng.choice([1, 2, 3, 5, 8, 16, 33, 64, 100, 257, 513])))
-    while n * dim0 < 16:        # a handful of elements per channel is a conditioning exercise, not a kernel test
-        n *= 2
-    return (n, c) + tuple(sp)
 
 
 @pytest.mark.parametrize("seed", [11, 12, 13, 14])

@@ -132,3 +132,29 @@ def check_layer_own_mask(d, got, what="", eps=1e-5, residual=None, slope=0.0):
         assert_close(got["dbeta"], s1, what + "dbeta", atol=ATOL + RTOL * rms1)
         assert_close(got["dgamma"], s2, what + "dgamma", atol=ATOL + RTOL * rms2 + cond * float(np.abs(dz).sum(axis=ax).max()))
     return int(flips.sum())
+
+
+def random_case(rng, max_elems=3e6):
+    """A random problem shape (N, C, spatial...): tiny, ragged and long unaligned rows, the networks' feature maps,
+    odd channel counts, one to a few hundred samples."""
+    mode = int(rng.integers(0, 4))
+    nd = int(rng.choice([1, 2, 2, 3]))
+    if mode == 0:
+        sp = [int(rng.integers(1, 9)) for _ in range(nd)]                  # tiny rows
+    elif mode == 1:
+        sp = [int(rng.integers(1, 40)) for _ in range(nd)]
+    elif mode == 2:
+        sp = [int(rng.choice([7, 14, 28, 56, 112, 8, 16, 32, 64]))] * 2      # the networks' feature maps
+    else:
+        sp = [int(rng.integers(1, 6)), int(rng.integers(50, 3000))]         # long, mostly unaligned rows
+    dim0 = int(np.prod(sp))
+    c = int(rng.choice([1, 2, 3, 4, 5, 8, 16, 31, 64, 96, 130, 260]))
+    n = int(min(max(1, int(max_elems // (dim0 * c))), rng.choice([1, 2, 3, 5, 8, 16, 33, 64, 100, 257, 513])))
+    while n * dim0 < 16:        # a handful of elements per channel is a conditioning exercise, not a kernel test
+        n *= 2
+    return (n, c) + tuple(sp)
+
+
+def random_shapes(seed, count, max_elems=3e6):
+    rng = np.random.default_rng(seed)
+    return [random_case(rng, max_elems) for _ in range(count)]
