@@ -113,9 +113,12 @@ __device__ __forceinline__ bool mbar_wait(unsigned long long *bar, uint32_t pari
     }
   }
 }
-// One lane waits for the whole warp; every lane gets the same answer.
+// Every lane gets the same answer.  The common case, a phase that is already complete (or completes while the
+// hardware holds the warp), is one instruction for the whole warp; only a wait that outlasts that is handed to
+// one lane, which polls with the time limit.
 __device__ __forceinline__ bool warp_wait(unsigned long long *bar, uint32_t parity, RingCtl *ctl, uint32_t *status, uint32_t bit)
 {
+  if (__all_sync(0xffffffffu, mbar_try(bar, parity))) return true;
   uint32_t ok = 1;
   if ((threadIdx.x & 31) == 0) ok = mbar_wait(bar, parity, ctl, status, bit) ? 1u : 0u;
   return __shfl_sync(0xffffffffu, ok, 0) != 0;
