@@ -265,7 +265,7 @@ __device__ __forceinline__ void warp_reduce_R(const FusedArgs &a, const RingGeom
     const float slope = a.neg_slope;      // activation: t * (t > 0 ? 1 : slope)
     float s1 = 0.f, s2 = 0.f, t1 = 0.f, t2 = 0.f;
     uint32_t i = 0;
-    for (; i + 2 <= cnt; i += 2, ax += 2 * kVecStride, ad += 2 * kVecStride) {
+    for (; DIR == 0 && i + 2 <= cnt; i += 2, ax += 2 * kVecStride, ad += 2 * kVecStride) {
       const Pack<4> x0 = lds128(ax), x1 = lds128(ax + kVecStride), g0 = lds128(ad), g1 = lds128(ad + kVecStride);
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
@@ -308,23 +308,29 @@ __device__ __forceinline__ void warp_apply_R(const FusedArgs &a, const RingGeom 
   const float mean = c0.x, scale = c0.y, beta = c0.z, cB = c1.x, cC = c1.y;
   const uint32_t per_row = tr.len / 4, nvec = per_row * tr.rows;
   const uint32_t cnt = tid < nvec ? (nvec - tid + kConsumers - 1) / kConsumers : 0;
-  const uint32_t mul = a.plan.div_mul;       // rows > 1 only occurs with whole rows, where per_row matches it
-  const bool one_row = tr.rows == 1;
   uint32_t ax = smem_u32(slot_x(sm, g, slot)) + tid * 16;
   uint32_t ad = ax + g.slot_floats * 4;
-  uint32_t j = tid;
-  float *po = out + 4 * (size_t)tid;           // running output pointer of the single-row case
-  for (uint32_t i = 0; i < cnt; ++i, ax += kVecStride, ad += kVecStride, j += kConsumers, po += 4 * kConsumers) {
-    const Pack<4> vx = lds128(ax);
-    float *dst = po;
-    if (!one_row) { const uint32_t r = fast_div(j, mul); dst = out + (size_t)r * rs + 4 * (size_t)(j - r * per_row); }
+  // The thread's vectors are tid, tid + kConsumers, ... of the tile's rows laid back to back; their places in
+  // global memory are found by walking (column, row) along, without a division or a 64-bit product per vector.
+  uint32_t col = tid, row = 0;
+  if (tr.rows > 1) { row = fast_div(tid, a.plan.div_mul); col = tid - row * per_row; }   // rows > 1 only occurs with whole rows, where per_row matches div_mul
+  float *dst = out + (size_t)row * rs + 4 * (size_t)col;
+  const uint32_t step_rows = tr.rows > 1 ? fast_div(kConsumers, a.plan.div_mul) : 0;     // kConsumers = step_rows * per_row + step_cols
+  const uint32_t step_cols = kConsumers - step_rows * per_row;
+  const size_t step_ptr = (size_t)step_rows * rs + 4 * (size_t)step_cols;               // floats from one vector of the thread to the next
+  const size_t wrap_ptr = rs - 4 * (size_t)per_row;                                      // on top of that when the column wraps into the next row
+  auto advance = [&]() {
+    dst += step_ptr; col += step_cols;
+    if (col >= per_row) { col -= per_row; dst += wrap_ptr; }
+  };
+  // one vector: o = activation(bn(x)) or the input gradient
+  auto one = [&](const Pack<4> &vx, const Pack<4> &vd, float *p) {
     Pack<4> o;
     if constexpr (DIR == 0) {
 #pragma unroll
       for (int e = 0; e < 4; ++e) { const float yb = fmaf(vx.v[e] - mean, scale, beta); o.v[e] = yb * (yb > 0.0f ? 1.0f : slope); }
     } else {
-      const Pack<4> vd = lds128(ad);
-      if (acc) o = Pack<4>::load(dst);
+      if (acc) o = Pack<4>::load(p);
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const float d = vx.v[e] - mean;
@@ -335,12 +341,30 @@ __device__ __forceinline__ void warp_apply_R(const FusedArgs &a, const RingGeom 
       }
     }
 #if ANODE_RING_STORE == 1
-    o.store_stream(dst);
+    o.store_stream(p);
 #elif ANODE_RING_STORE == 2
-    *reinterpret_cast<float4 *>(dst) = make_float4(o.v[0], o.v[1], o.v[2], o.v[3]);
+    *reinterpret_cast<float4 *>(p) = make_float4(o.v[0], o.v[1], o.v[2], o.v[3]);
 #else
-    o.store(dst, drop);
+    o.store(p, drop);
 #endif
+  };
+  uint32_t i = 0;
+  for (; i + 2 <= cnt; i += 2, ax += 2 * kVecStride, ad += 2 * kVecStride) {
+    // two vectors' shared loads in flight before the first is used
+    const Pack<4> x0 = lds128(ax), x1 = lds128(ax + kVecStride);
+    Pack<4> d0 = x0, d1 = x1;
+    if constexpr (DIR == 1) { d0 = lds128(ad); d1 = lds128(ad + kVecStride); }
+    float *p0 = dst; advance();
+    float *p1 = dst; advance();
+    one(x0, d0, p0);
+    one(x1, d1, p1);
+  }
+  for (; i < cnt; ++i, ax += kVecStride, ad += kVecStride) {
+    const Pack<4> x0 = lds128(ax);
+    Pack<4> d0 = x0;
+    if constexpr (DIR == 1) d0 = lds128(ad);
+    one(x0, d0, dst);
+    advance();
   }
   __syncwarp();
   if (lane == 0) { mbar_arrive(&ctl->empty[slot]); mbar_arrive(&ctl->coef_empty[coef_q]); }
@@ -454,7 +478,9 @@ __device__ __forceinline__ void st_relaxed_sys_u64(unsigned long long *p, unsign
 {
   asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
 }
-constexpr int kPullRegs = 8;      // partial words per lane per round (256 tiles per round)
+// partial words per lane per round of pull_merge_unit: the backward pass has four times the tiles per unit of the
+// forward pass (smaller tiles), and a round costs a trip to L2; the forward merge does more arithmetic per word
+constexpr int kPullRegsFwd = 8, kPullRegsBwd = 16;
 
 // Whole warp.  Returns false when the wait ran out (abort raised).  On success c0 / c1 hold the
 // unit's coefficients in every lane; `owner` makes lane 0 write the per-channel outputs.
@@ -462,6 +488,7 @@ template <int DIR>
 __device__ __forceinline__ bool pull_merge_unit(const FusedArgs &a, RingCtl *ctl, uint32_t *status, uint32_t u, bool owner,
                                                 float4 &c0, float4 &c1)
 {
+  constexpr int kPullRegs = DIR == 0 ? kPullRegsFwd : kPullRegsBwd;
   const Plan &P = a.plan;
   const uint32_t lane = threadIdx.x & 31, T = P.tiles_per_unit;
   const unsigned long long *buf = tag_buf(a, ctl->parity) + (size_t)u * T;
@@ -693,6 +720,8 @@ __global__ void __launch_bounds__(kRingThreads, 1) bn_ring_kernel(const FusedArg
     while (ok && sc.next_range(P, kind, tr)) {
       ++k;
       if (++slot == g.slots) { slot = 0; par ^= 1u; }
+      // (one lane polls here: a producer that reacts sooner was measured slower where the window between the two
+      // visits exceeds what L2 keeps, and hardly faster elsewhere)
       uint32_t okw = 1;
       if (lane == 0) okw = mbar_wait(&ctl->empty[slot], par ^ 1u, ctl, status, ANODE_ST_WAIT_STATS) ? 1u : 0u;
       ok = __shfl_sync(0xffffffffu, okw, 0) != 0;     // one lane decides for the warp
