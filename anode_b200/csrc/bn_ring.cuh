@@ -263,33 +263,22 @@ __device__ __forceinline__ void warp_reduce_R(const FusedArgs &a, const RingGeom
     const float4 cf = slot_side<1>(sm, g, slot)[0];
     const float mean = cf.x, scale = cf.y, beta = cf.z;
     const float slope = a.neg_slope;      // activation: t * (t > 0 ? 1 : slope)
-    float s1 = 0.f, s2 = 0.f, t1 = 0.f, t2 = 0.f;
-    uint32_t i = 0;
-    for (; DIR == 0 && i + 2 <= cnt; i += 2, ax += 2 * kVecStride, ad += 2 * kVecStride) {
-      const Pack<4> x0 = lds128(ax), x1 = lds128(ax + kVecStride), g0 = lds128(ad), g1 = lds128(ad + kVecStride);
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const float d0 = x0.v[e] - mean, d1 = x1.v[e] - mean;
-        const float y0 = fmaf(d0, scale, beta), y1 = fmaf(d1, scale, beta);
-        // dz = dy * (float)(y > 0)  (routines_gpu/flat_map.cu:191-192)
-        const float z0 = g0.v[e] * (y0 > 0.0f ? 1.0f : slope);
-        const float z1 = g1.v[e] * (y1 > 0.0f ? 1.0f : slope);
-        s1 += z0; s2 = fmaf(z0, d0, s2); t1 += z1; t2 = fmaf(z1, d1, t2);
-      }
-    }
-    for (; i < cnt; ++i, ax += kVecStride, ad += kVecStride) {
+    float s1 = 0.f, s2 = 0.f;
+    // (one vector per tensor at a time: with two in flight the sixteen warps of this pass were measured slower)
+    for (uint32_t i = 0; i < cnt; ++i, ax += kVecStride, ad += kVecStride) {
       const Pack<4> x0 = lds128(ax), g0 = lds128(ad);
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const float d0 = x0.v[e] - mean;
         const float y0 = fmaf(d0, scale, beta);
+        // dz = dy * (float)(y > 0)  (routines_gpu/flat_map.cu:191-192)
         const float z0 = g0.v[e] * (y0 > 0.0f ? 1.0f : slope);
         s1 += z0; s2 = fmaf(z0, d0, s2);
       }
     }
     __syncwarp();
     if (lane == 0) mbar_arrive(&ctl->empty[slot]);
-    s1 = warp_sum(s1 + t1); s2 = warp_sum(s2 + t2);
+    s1 = warp_sum(s1); s2 = warp_sum(s2);
     if (lane == 0) res[warp] = make_float4(s1, s2, 0.f, 0.f);
   }
 }
@@ -348,18 +337,7 @@ __device__ __forceinline__ void warp_apply_R(const FusedArgs &a, const RingGeom 
     o.store(p, drop);
 #endif
   };
-  uint32_t i = 0;
-  for (; i + 2 <= cnt; i += 2, ax += 2 * kVecStride, ad += 2 * kVecStride) {
-    // two vectors' shared loads in flight before the first is used
-    const Pack<4> x0 = lds128(ax), x1 = lds128(ax + kVecStride);
-    Pack<4> d0 = x0, d1 = x1;
-    if constexpr (DIR == 1) { d0 = lds128(ad); d1 = lds128(ad + kVecStride); }
-    float *p0 = dst; advance();
-    float *p1 = dst; advance();
-    one(x0, d0, p0);
-    one(x1, d1, p1);
-  }
-  for (; i < cnt; ++i, ax += kVecStride, ad += kVecStride) {
+  for (uint32_t i = 0; i < cnt; ++i, ax += kVecStride, ad += kVecStride) {
     const Pack<4> x0 = lds128(ax);
     Pack<4> d0 = x0;
     if constexpr (DIR == 1) d0 = lds128(ad);
