@@ -45,6 +45,14 @@ __device__ __forceinline__ uint64_t policy_keep()
   asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
   return p;
 }
+// keep for a fraction of the lines (chosen by address), drop for the rest: for a working set larger than what
+// L2 can hold, so that the kept part stays instead of all of it cycling through
+__device__ __forceinline__ uint64_t policy_keep_fraction(float f)
+{
+  uint64_t p;
+  asm volatile("createpolicy.fractional.L2::evict_last.L2::evict_first.b64 %0, %1;" : "=l"(p) : "f"(f));
+  return p;
+}
 __device__ __forceinline__ uint64_t policy_drop()
 {
   uint64_t p;

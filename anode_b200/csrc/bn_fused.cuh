@@ -722,6 +722,7 @@ constexpr uint32_t kMaxSlots = 8;
 constexpr uint32_t kRingCtlBytes = 1024;   // room reserved for the kernel's barrier block (RingCtl)
 struct RingGeom {
   uint32_t slots, slot_floats, slot_stride, res_stride, off_res, off_coef, off_slots, smem_bytes;
+  float keep_frac;         // fused mode: fraction of the reduce visits' lines loaded with the L2 "keep" priority
 };
 
 }  // namespace anode_b200

@@ -675,7 +675,8 @@ __global__ void __launch_bounds__(kRingThreads, 1) bn_ring_kernel(const FusedArg
     }
   } else if (warp == kConsumers / 32) {
     // ------------------------------------------------------------------ producer
-    const uint64_t keep = policy_keep(), drop = policy_drop();
+    // where the window between the two visits exceeds what L2 keeps, only the fraction that fits is marked "keep"
+    const uint64_t keep = g.keep_frac < 1.0f ? policy_keep_fraction(g.keep_frac) : policy_keep(), drop = policy_drop();
     const uint64_t rs = (uint64_t)P.C * P.dim0;
     uint32_t k = 0;
     uint32_t slot = g.slots - 1, par = 1;
