@@ -93,6 +93,7 @@ SIGNATURES = {
     "anode_gpu_batch_norm_fused_plan_walk":
         (c_int, _D + [c_int, u32, u32, u32, u32, u32, ctypes.POINTER(ctypes.c_uint64)]),
     "anode_gpu_batch_norm_segres_geometry": (c_int, _D + [c_int, ctypes.POINTER(u32)]),
+    "anode_gpu_batch_norm_tiled_geometry": (c_int, _D + [c_int, ctypes.POINTER(u32)]),
     "anode_gpu_batch_norm_fused_kernel_kind": (c_int, _D + [c_int]),
     "anode_gpu_batch_norm_add_act_fused_kernel_kind": (c_int, _D + [c_int]),
     "anode_gpu_batch_norm_fused_set_wait_limit_ms": (c_int, [u32]),

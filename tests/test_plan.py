@@ -156,3 +156,33 @@ def test_host_step_block_count_and_staging_size():
     rc = lib.anode_gpu_batch_norm_relu_fused_step_host_3d1_packed_f32(d0, c, n, 1e-5, 0.1, 1, None, None, None, None, None, None,
                                                                       None, None, None, None, None, None, None, 0, 0, None, None)
     assert rc == -1
+
+
+def tiled_geometry(d0, c, n, direction):
+    out = (ctypes.c_uint32 * 9)()
+    assert _lib.load().anode_gpu_batch_norm_tiled_geometry(d0, c, n, direction, out) == 0
+    keys = ["applies", "rows", "piece", "tiles_per_unit", "slots", "slot_bytes", "smem", "window_kib", "keep_permille"]
+    return dict(zip(keys, list(out)))
+
+
+def test_tiled_kernel_geometry_follows_the_window():
+    """Backward pass: three slots of larger tiles while the window between a tile's two visits stays within
+    what L2 keeps (48 MiB), four slots of the standard tiles beyond; and only the part of a larger window that
+    fits is loaded with the keep priority.  (148 SMs are assumed where no device can be asked.)"""
+    small = tiled_geometry(3136, 256, 256, 1)        # one GPU's share of config 3 at eight GPUs
+    mid = tiled_geometry(3136, 256, 512, 1)
+    big = tiled_geometry(3136, 256, 1024, 1)
+    full = tiled_geometry(3136, 256, 2048, 1)        # config 3 on one GPU
+    assert (small["rows"], small["slots"]) == (3, 3) and (mid["rows"], mid["slots"]) == (3, 3)
+    assert (big["rows"], big["slots"]) == (2, 4) and (full["rows"], full["slots"]) == (2, 4)
+    for g in (small, mid, big):
+        assert g["window_kib"] <= 48 * 1024 and g["keep_permille"] == 1000
+    assert full["window_kib"] > 48 * 1024
+    assert abs(full["keep_permille"] - 1000 * 48 * 1024 / full["window_kib"]) <= 1
+    # the forward pass has one geometry; everything fits the 227 KB of shared memory; short rows are not this kernel's
+    for n in (256, 512, 1024, 2048):
+        f = tiled_geometry(3136, 256, n, 0)
+        assert (f["rows"], f["slots"]) == (5, 3) and f["smem"] <= 227 * 1024
+    for g in (small, mid, big, full):
+        assert g["smem"] <= 227 * 1024 and g["slots"] * g["slot_bytes"] < g["smem"]
+    assert tiled_geometry(49, 2048, 1024, 0)["applies"] == 0
