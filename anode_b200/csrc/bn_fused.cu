@@ -602,20 +602,21 @@ extern "C" int anode_gpu_batch_norm_fused_set_kernel(int kernel)
 }
 
 // ---- diagnostics: geometry of the tiled kernel for a shape (no GPU needed) ----------------------
-// out (9 values): applies, rows per tile, floats per row piece, tiles per unit, slots, bytes per slot, dynamic
+// out (12 values): applies, rows per tile, floats per row piece, tiles per unit, slots, bytes per slot, dynamic
 // shared memory bytes, KiB between a tile's two visits, the fraction (in 1/1000) of that window loaded with the
-// "keep" priority
+// "keep" priority, blocks, steps between a tile's two visits, tiles
 extern "C" int anode_gpu_batch_norm_tiled_geometry(uint32_t dim0, uint32_t dim1, uint32_t dim2, int dir, uint32_t *out)
 {
   using namespace anode_b200;
   if (!out || (dir != 0 && dir != 1) || check_dims(dim0, dim1, dim2)) return ANODE_E_DIMS;
   Plan p; RingGeom g;
-  for (int i = 0; i < 9; ++i) out[i] = 0;
+  for (int i = 0; i < 12; ++i) out[i] = 0;
   if (!ring_plan_for(dim0, dim1, dim2, true, dir, p, g)) return ANODE_OK;
   const uint64_t window = ring_window_bytes(p, dir);
   out[0] = 1; out[1] = p.rows_per_tile; out[2] = p.piece_len; out[3] = p.tiles_per_unit; out[4] = g.slots;
   out[5] = g.slot_stride; out[6] = g.smem_bytes; out[7] = (uint32_t)(window >> 10);
   out[8] = window > kRingLargeWindowMax ? (uint32_t)(1000.0 * (double)kRingLargeWindowMax / (double)window) : 1000u;
+  out[9] = p.grid; out[10] = p.lookahead_steps; out[11] = p.total_tiles;
   return ANODE_OK;
 }
 

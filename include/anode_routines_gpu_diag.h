@@ -39,9 +39,9 @@ int anode_gpu_batch_norm_fused_plan_walk(uint32_t dim0, uint32_t dim1, uint32_t 
 int anode_gpu_batch_norm_segres_geometry(uint32_t dim0, uint32_t dim1, uint32_t dim2, int dir, uint32_t *out);
 
 /* Geometry of the tiled kernel (bn_ring.cuh) for direction `dir` of a fused call on 16-byte aligned tensors.
- * out (9 values): applies, rows per tile, floats per row piece, tiles per unit, slots, bytes per slot, dynamic
- * shared memory bytes, KiB between a tile's two visits (what L2 has to hold), and the fraction (in 1/1000) of
- * that window loaded with the "keep" priority. */
+ * out (12 values): applies, rows per tile, floats per row piece, tiles per unit, slots, bytes per slot, dynamic
+ * shared memory bytes, KiB between a tile's two visits (what L2 has to hold), the fraction (in 1/1000) of
+ * that window loaded with the "keep" priority, thread blocks, steps between a tile's two visits, tiles. */
 int anode_gpu_batch_norm_tiled_geometry(uint32_t dim0, uint32_t dim1, uint32_t dim2, int dir, uint32_t *out);
 
 /* Plan of the slice-resident kernel for `planes` tensors per shared-memory slot.  out (16 values): applies,

@@ -159,9 +159,10 @@ def test_host_step_block_count_and_staging_size():
 
 
 def tiled_geometry(d0, c, n, direction):
-    out = (ctypes.c_uint32 * 9)()
+    out = (ctypes.c_uint32 * 12)()
     assert _lib.load().anode_gpu_batch_norm_tiled_geometry(d0, c, n, direction, out) == 0
-    keys = ["applies", "rows", "piece", "tiles_per_unit", "slots", "slot_bytes", "smem", "window_kib", "keep_permille"]
+    keys = ["applies", "rows", "piece", "tiles_per_unit", "slots", "slot_bytes", "smem", "window_kib", "keep_permille",
+            "grid", "lookahead", "tiles"]
     return dict(zip(keys, list(out)))
 
 
@@ -186,3 +187,60 @@ def test_tiled_kernel_geometry_follows_the_window():
     for g in (small, mid, big, full):
         assert g["smem"] <= 227 * 1024 and g["slots"] * g["slot_bytes"] < g["smem"]
     assert tiled_geometry(49, 2048, 1024, 0)["applies"] == 0
+
+
+def simulate_tiled_schedule(tiles, per_unit, grid, look):
+    """Every block walks its visits in order (reduce tile b + s*G, apply tile b + (s - look)*G); an apply visit
+    can only be served once every tile of its unit has been reduced.  Returns True when all blocks finish."""
+    units = tiles // per_unit
+    reduced = [0] * units
+    seq = []
+    for b in range(grid):
+        mine = range(b, tiles, grid)
+        n = len(mine)
+        v = []
+        for s in range(n + look):
+            if s < n:
+                v.append((0, b + s * grid))
+            if s >= look:
+                v.append((1, b + (s - look) * grid))
+        seq.append(v)
+    pos = [0] * grid
+    progress = True
+    while progress:
+        progress = False
+        for b in range(grid):
+            v = seq[b]
+            while pos[b] < len(v):
+                kind, t = v[pos[b]]
+                u = t // per_unit
+                if kind == 0:
+                    reduced[u] += 1
+                elif reduced[u] < per_unit:
+                    break
+                pos[b] += 1
+                progress = True
+    return all(pos[b] == len(seq[b]) for b in range(grid))
+
+
+def test_tiled_schedule_cannot_wait_in_a_cycle():
+    """The fixed schedule of the tiled kernel with the planner's distance between a tile's two visits, on the
+    geometries the planner picks for a spread of shapes (both backward tile choices among them): a block that
+    waits for a unit's statistics never holds back a reduce visit of that unit.  One step less does deadlock."""
+    shapes = [(3136, 8, 64), (3136, 16, 300), (3136, 4, 2048), (12544, 6, 40), (784, 12, 256), (1024, 5, 77),
+              (65536, 3, 4), (3136, 2, 1)]
+    seen = set()
+    for d0, c, n in shapes:
+        for direction in (0, 1):
+            g = tiled_geometry(d0, c, n, direction)
+            if not g["applies"]:
+                continue
+            seen.add((g["rows"], g["slots"]))
+            assert g["tiles"] % g["tiles_per_unit"] == 0 and g["lookahead"] * g["grid"] >= g["tiles_per_unit"]
+            assert simulate_tiled_schedule(g["tiles"], g["tiles_per_unit"], g["grid"], g["lookahead"]), (d0, c, n, direction)
+    assert len(seen) >= 3
+    # what the rule guards against: with too few steps in between, blocks wait for tiles that sit behind their own
+    # apply visits (a step's reduce visit comes before its apply visit, so (look + 1) * grid >= tiles per unit is
+    # the exact bound; the planner asks for one step more, and for the slack on top)
+    assert not simulate_tiled_schedule(tiles=8 * 40, per_unit=40, grid=8, look=3)
+    assert simulate_tiled_schedule(tiles=8 * 40, per_unit=40, grid=8, look=4)
